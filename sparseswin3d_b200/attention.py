@@ -1,0 +1,115 @@
+"""Fused W-MSA / SW-MSA: the drop-in for upstream's ``WindowAttentionSparse``
+(sparse_swin/swin3d_base.py:589-677)."""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from ._lib import check, dtype_code, lib, ptr, stream_ptr
+from .window import WindowPlan, bucket_windows
+
+
+def default_tile_rows(num_heads: int, head_dim: int, dtype: torch.dtype) -> int:
+    return int(lib.ssw_default_tile_rows(num_heads, head_dim, dtype_code(dtype)))
+
+
+def window_attention_fused(qkv: torch.Tensor, plan: WindowPlan, table: torch.Tensor, scale: float,
+                           use_mask: bool = False, return_attn: bool = False, out: Optional[torch.Tensor] = None):
+    """Everything between the two Linear layers of WindowAttentionSparse.forward
+    (swin3d_base.py:659-675) in one kernel launch.
+
+    qkv    [N, 3, H, hd] (or [N, 3*H*hd]) fp32 / bf16 / fp16, contiguous, CUDA
+    plan   from `bucket_windows` (built with tile_rows = default_tile_rows(H, hd, dtype))
+    table  relative_position_bias_table [(2Wz-1)(2Wy-1)(2Wx-1), H]
+    Returns out [N, H*hd] in the caller's voxel order; with return_attn=True also the post-softmax
+    COO values in upstream order (window, head, pos_i, pos_j) — that variant synchronises once to
+    size the buffer."""
+    if not qkv.is_cuda:
+        raise _lib.SswError("qkv must be a CUDA tensor (there is no CPU path)")
+    if qkv.dim() != 4 or qkv.shape[1] != 3:
+        raise _lib.SswError("qkv must be [N, 3, heads, head_dim]")
+    if not qkv.is_contiguous():
+        raise _lib.SswError("qkv must be contiguous")
+    N, _, H, hd = qkv.shape
+    if N != plan.layout.n_vox:
+        raise _lib.SswError(f"plan was built for {plan.layout.n_vox} voxels, qkv has {N}")
+    if use_mask and not plan.has_regions:
+        raise _lib.SswError("use_mask=True but the plan carries no region ids (no shift / no mask given)")
+    table = table.detach()
+    if table.dtype != torch.float32 or not table.is_contiguous():
+        table = table.float().contiguous()
+    rw = plan.rpb_window
+    if table.shape != ((2 * rw[0] - 1) * (2 * rw[1] - 1) * (2 * rw[2] - 1), H):
+        raise _lib.SswError(f"bias table shape {tuple(table.shape)} does not match window {rw} and {H} heads")
+    if out is None:
+        out = torch.empty((N, H * hd), dtype=qkv.dtype, device=qkv.device)
+    attn = None
+    if return_attn:
+        st = plan.stats()
+        if st["error"] & _lib.DEV_COO_RANGE or st["sum_c2"] * H >= 2 ** 31:
+            raise _lib.SswError("sum c^2 * heads leaves the int32 domain of the COO layout")
+        attn = torch.empty(st["sum_c2"] * H, dtype=qkv.dtype, device=qkv.device)
+    rwc = (_lib.i32 * 3)(*rw)
+    check(lib.ssw_attn_fused(ptr(qkv), dtype_code(qkv.dtype), H, hd, plan.layout, ptr(plan.plan), ptr(table), rwc,
+                             float(scale), int(bool(use_mask)), ptr(out), ptr(attn), stream_ptr(qkv.device)),
+          "ssw_attn_fused")
+    return (out, attn) if return_attn else out
+
+
+class WindowAttentionSparse(nn.Module):
+    """Window multi-head self-attention with relative position bias over sparse voxel windows.
+
+    Same constructor, parameters (``qkv``, ``proj``, ``relative_position_bias_table``) and buffer
+    (``relative_position_index``) as upstream (swin3d_base.py:597-652), so a state_dict moves across
+    unchanged.  ``forward(x, mask)`` accepts what upstream's forward accepts: an object with
+    ``features`` [N,C], ``indices`` [N,2] int32 (window, pos), ``batch_size`` (all windows, empty
+    ones included), ``spatial_shape`` (n,) and ``replace_feature`` (swin3d_base.py:654-677).
+    Inference only: the fused kernel has no autograd."""
+
+    def __init__(self, dim: int, num_heads: int, window_size: Sequence[int], qkv_bias: bool = False,
+                 attn_drop: float = 0.0, proj_drop: float = 0.0) -> None:
+        super().__init__()
+        if len(window_size) != 3:
+            raise ValueError("window_size must have three entries")
+        self.dim, self.window_size, self.num_heads = dim, tuple(window_size), num_heads
+        head_dim = dim // num_heads
+        self.scale = head_dim ** -0.5
+        ws = self.window_size
+        self.relative_position_bias_table = nn.Parameter(
+            torch.zeros((2 * ws[0] - 1) * (2 * ws[1] - 1) * (2 * ws[2] - 1), num_heads))
+        coords = torch.stack(torch.meshgrid(*(torch.arange(w) for w in ws), indexing="ij"))
+        cf = torch.flatten(coords, 1)
+        rel = (cf[:, :, None] - cf[:, None, :]).permute(1, 2, 0).contiguous()
+        rel[:, :, 0] += ws[0] - 1
+        rel[:, :, 1] += ws[1] - 1
+        rel[:, :, 2] += ws[2] - 1
+        rel[:, :, 0] *= (2 * ws[1] - 1) * (2 * ws[2] - 1)
+        rel[:, :, 1] *= 2 * ws[2] - 1
+        self.register_buffer("relative_position_index", rel.sum(-1))
+        self.qkv = nn.Linear(dim, dim * 3, bias=qkv_bias)
+        self.attn_drop = nn.Dropout(attn_drop)  # constructed but never applied upstream either
+        self.proj = nn.Linear(dim, dim)
+        self.proj_drop = nn.Dropout(proj_drop)
+        nn.init.trunc_normal_(self.relative_position_bias_table, std=0.02, a=-2.0, b=2.0)
+
+    def tile_rows(self, dtype: torch.dtype) -> int:
+        return default_tile_rows(self.num_heads, self.dim // self.num_heads, dtype)
+
+    def plan(self, x, mask: Optional[torch.Tensor], dtype: torch.dtype) -> WindowPlan:
+        return bucket_windows(indices=x.indices, n_windows=int(x.batch_size), n_per_window=int(x.spatial_shape[0]),
+                              mask=mask, rpb_window=self.window_size, tile_rows=self.tile_rows(dtype))
+
+    @torch.no_grad()
+    def forward_features(self, features: torch.Tensor, plan: WindowPlan, use_mask: bool) -> torch.Tensor:
+        qkv = self.qkv(features).reshape(-1, 3, self.num_heads, self.dim // self.num_heads)
+        core = window_attention_fused(qkv, plan, self.relative_position_bias_table, self.scale, use_mask)
+        return self.proj_drop(self.proj(core))
+
+    @torch.no_grad()
+    def forward(self, x, mask, plan: Optional[WindowPlan] = None):
+        if plan is None:
+            plan = self.plan(x, mask, x.features.dtype)
+        return x.replace_feature(self.forward_features(x.features, plan, mask is not None))

@@ -1,0 +1,42 @@
+"""Seeded inputs shared by the parity tests (CPU tensors; tests move them to the device)."""
+from __future__ import annotations
+
+import torch
+
+from oracle import ssw_oracle as O
+from sparseswin3d_b200 import scenes
+
+
+def make_case(n_vox=3000, grid=40, heads=3, head_dim=32, window=(7, 7, 7), shift=(0, 0, 0), seed=0, batch=1,
+              table_std=0.5, dims=None):
+    """Uniform random voxels in a cube (or `dims`), random qkv and bias table; returns a dict with
+    everything the oracle and the CUDA path need."""
+    g = torch.Generator().manual_seed(seed)
+    import numpy as np
+
+    if dims is None:
+        dims = (grid, grid, grid)
+    rng = np.random.default_rng(seed)
+    per = []
+    for b in range(batch):
+        flat = rng.choice(dims[0] * dims[1] * dims[2], size=n_vox, replace=False)
+        z, y, x = np.unravel_index(flat, dims)
+        per.append(np.stack([np.full_like(z, b), z, y, x], 1))
+    coords = torch.from_numpy(np.concatenate(per).astype(np.int32))
+    idx, Bw, n, ws, ss, dp = O.window_keys(coords, batch, dims, window, shift)
+    N = coords.shape[0]
+    qkv = torch.randn(N, 3, heads, head_dim, generator=g)
+    table = torch.randn((2 * window[0] - 1) * (2 * window[1] - 1) * (2 * window[2] - 1), heads, generator=g) * table_std
+    rpi = O.relative_position_index(window)
+    mask = O.compute_mask(dp, ws, ss) if any(s > 0 for s in ss) else None
+    return dict(coords=coords, dims=dims, batch=batch, window=window, shift=shift, indices=idx, n_windows=Bw, n=n,
+                ws=ws, ss=ss, dims_p=dp, qkv=qkv, table=table, rpi=rpi, mask=mask, heads=heads, head_dim=head_dim,
+                scale=head_dim ** -0.5)
+
+
+def rel_err(x: torch.Tensor, ref: torch.Tensor) -> float:
+    """max |x - ref| / max(|ref|, rms(ref)) — the tolerance form used for value parity."""
+    ref = ref.double()
+    x = x.double()
+    rms = ref.pow(2).mean().sqrt().clamp_min(1e-30)
+    return float(((x - ref).abs() / torch.maximum(ref.abs(), rms)).max()) if ref.numel() else 0.0

@@ -1,0 +1,107 @@
+"""Parity of the CUDA bucketing + fused attention path against the CPU oracle (through the C ABI)."""
+import pytest
+import torch
+
+from oracle import ssw_oracle as O
+from tests.cases import make_case, rel_err
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5   # |x-ref| <= tol * max(|ref|, rms(ref)), the fp32 bound of the task statement
+BF16_TOL = 2e-2   # same form, bf16 inputs/outputs against the fp32 oracle
+
+
+def _plan(case, dev, dtype, from_coords=True, tile=None):
+    from sparseswin3d_b200 import attention, window
+
+    tile = tile or attention.default_tile_rows(case["heads"], case["head_dim"], dtype)
+    if from_coords:
+        g = window.resolve_geometry(case["batch"], case["dims"], case["window"], case["shift"])
+        return window.bucket_windows(coords=case["coords"].to(dev), geom=g, rpb_window=case["window"], tile_rows=tile)
+    mask = case["mask"].to(dev) if case["mask"] is not None else None
+    return window.bucket_windows(indices=case["indices"].to(dev), n_windows=case["n_windows"], n_per_window=case["n"],
+                                 mask=mask, rpb_window=case["window"], tile_rows=tile)
+
+
+def _check_plan(case, plan):
+    idx = case["indices"].long()
+    key = idx[:, 0] * case["n"] + idx[:, 1]
+    order = torch.argsort(key)
+    st = plan.stats()
+    assert st["error"] == 0
+    assert st["voxels"] == idx.shape[0]
+    perm = plan.perm.cpu().long()
+    assert torch.equal(perm, order)                      # sorted row -> voxel, bit exact
+    arg_sort = O.return_inverse(O.flatten_indices(case["indices"].T.contiguous(), [case["n_windows"], case["n"]]), -1)[0]
+    assert torch.equal(plan.inv_perm.cpu(), arg_sort)     # upstream's arg_sort (swin3d_base.py:674)
+    wins, counts = torch.unique(idx[:, 0], return_counts=True)
+    assert st["windows"] == wins.numel()
+    assert torch.equal(plan.win_id[: wins.numel()].cpu().long(), wins)
+    assert torch.equal(plan.occupancy().cpu().long(), counts)
+    assert st["sum_c2"] == int((counts ** 2).sum())
+    assert st["c_max"] == int(counts.max())
+    # pack order is a permutation of the voxels
+    assert torch.equal(torch.sort(plan.pack_perm.cpu().long())[0], torch.arange(idx.shape[0]))
+
+
+@pytest.mark.parametrize("shift", [(0, 0, 0), (3, 3, 3)])
+@pytest.mark.parametrize("from_coords", [True, False])
+def test_bucket_and_fused_fp32(shift, from_coords):
+    from sparseswin3d_b200 import attention
+
+    dev = torch.device("cuda:0")
+    case = make_case(n_vox=3000, grid=40, shift=shift, seed=3)
+    plan = _plan(case, dev, torch.float32, from_coords)
+    _check_plan(case, plan)
+    ref, attn_ref = O.window_attention_core(case["qkv"], case["indices"], case["n_windows"], case["n"], case["scale"],
+                                            case["table"], case["rpi"], case["mask"])
+    out, attn = attention.window_attention_fused(case["qkv"].to(dev), plan, case["table"].to(dev), case["scale"],
+                                                 use_mask=case["mask"] is not None, return_attn=True)
+    torch.cuda.synchronize()
+    assert plan.stats()["error"] == 0
+    assert rel_err(out.cpu(), ref) <= FP32_TOL
+    assert attn.numel() == attn_ref.values.numel()
+    assert rel_err(attn.cpu(), attn_ref.values) <= FP32_TOL
+    out2 = attention.window_attention_fused(case["qkv"].to(dev), plan, case["table"].to(dev), case["scale"],
+                                            use_mask=case["mask"] is not None)
+    assert torch.equal(out2, out)  # the emitting variant and the plain one agree bit for bit
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, BF16_TOL), (torch.float16, 2e-3)])
+def test_fused_half_types(dtype, tol):
+    from sparseswin3d_b200 import attention
+
+    dev = torch.device("cuda:0")
+    case = make_case(n_vox=3000, grid=40, shift=(3, 3, 3), seed=4)
+    plan = _plan(case, dev, dtype)
+    qkv = case["qkv"].to(dtype)
+    ref, _ = O.window_attention_core(qkv.float(), case["indices"], case["n_windows"], case["n"], case["scale"],
+                                     case["table"], case["rpi"], case["mask"])
+    out = attention.window_attention_fused(qkv.to(dev), plan, case["table"].to(dev), case["scale"], use_mask=True)
+    assert out.dtype == dtype
+    assert rel_err(out.float().cpu(), ref) <= tol
+
+
+@pytest.mark.parametrize("n_vox,grid,heads,hd,window", [
+    (1, 8, 3, 32, (7, 7, 7)),          # single voxel
+    (40, 7, 3, 32, (7, 7, 7)),         # everything in one window
+    (343, 7, 2, 16, (7, 7, 7)),        # one completely full window (c = 343 > tile)
+    (2000, 14, 6, 16, (7, 7, 7)),      # dense-ish windows, several key tiles
+    (500, 64, 12, 16, (7, 7, 7)),      # singletons mostly, many heads
+    (3000, 18, 6, 32, (9, 9, 9)),      # window 9
+    (600, 30, 3, 32, (5, 6, 7)),       # anisotropic window
+])
+@pytest.mark.parametrize("shift", [False, True])
+def test_fused_shapes(n_vox, grid, heads, hd, window, shift):
+    from sparseswin3d_b200 import attention
+
+    dev = torch.device("cuda:0")
+    sh = tuple(w // 2 for w in window) if shift else (0, 0, 0)
+    case = make_case(n_vox=n_vox, grid=grid, heads=heads, head_dim=hd, window=window, shift=sh, seed=n_vox)
+    plan = _plan(case, dev, torch.float32)
+    _check_plan(case, plan)
+    ref = O.dense_window_attention(case["qkv"], case["indices"], case["scale"], case["table"], case["rpi"], case["mask"])
+    out = attention.window_attention_fused(case["qkv"].to(dev), plan, case["table"].to(dev), case["scale"],
+                                           use_mask=case["mask"] is not None)
+    assert plan.stats()["error"] == 0
+    assert rel_err(out.cpu(), ref) <= FP32_TOL
