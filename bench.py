@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Throughput of the sparse window-attention hot path on B200: voxels/s through W-MSA + SW-MSA.
+
+One *step* = one W-MSA pass (no shift) followed by one SW-MSA pass (shift 3, with the shift mask)
+over one synthetic room scene of 150 000 voxels (C = 96, 3 heads x 32, window 7^3): for each pass,
+window bucketing from the raw voxel coordinates and the fused attention kernel.  Every voxel is
+counted once per pass, so one step moves 2 * N voxels.  With --gpus N every rank works on its own
+scene (seed = rank): weak scaling, no collective on the data path.
+
+    python bench.py                       # 1 GPU, defaults
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8
+    python bench.py --impl reference      # the CPU restatement of upstream, timed on the host cores
+
+Prints one JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "voxels/sec through W-MSA+SW-MSA"
+UNIT = "voxels/s"
+N_VOX = 150_000
+HEADS, HEAD_DIM, WINDOW, SHIFT = 3, 32, (7, 7, 7), (3, 3, 3)
+C = HEADS * HEAD_DIM
+KERNELS_PER_PASS = 6  # k_count, k_reduce, k_compact, k_order, k_scatter, k_attn_fused
+# DRAM bytes one k_attn_fused launch moves on this workload (dram__bytes_read.sum + dram__bytes_write.sum
+# of an ncu capture, see profiles/); None until a capture exists for the dtype.
+NCU_TRAFFIC_BYTES = {"f32": None, "bf16": None}
+
+
+def algorithmic_bytes_per_voxel(elt: int) -> int:
+    """q, k, v rows in, out row out, int32 (window, pos) and one int32 permutation entry."""
+    return 4 * C * elt + 12
+
+
+def measured_peak_gbs():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                for n, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(seed: int, dtype: torch.dtype, device, n_sets: int):
+    from sparseswin3d_b200 import scenes
+
+    coords, dims = scenes.room_scene(N_VOX, seed=seed)
+    g = torch.Generator().manual_seed(1000 + seed)
+    qkv_host = [torch.randn(N_VOX, 3, HEADS, HEAD_DIM, generator=g).to(dtype).pin_memory() for _ in range(n_sets)]
+    coords_host = torch.from_numpy(coords).pin_memory()
+    table = (torch.randn((2 * WINDOW[0] - 1) ** 3, HEADS, generator=g) * 0.02).to(device)
+    return coords_host, dims, qkv_host, table
+
+
+def run_ours(args):
+    from sparseswin3d_b200 import _lib, attention, window
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[args.dtype]
+    elt = 4 if args.dtype == "f32" else 2
+    n_sets = 3  # rotate buffer sets so that no step finds its inputs in the 126 MB L2
+    coords_h, dims, qkv_h, table = make_inputs(rank, dtype, dev, n_sets)
+    coords = coords_h.to(dev)
+    qkv = [q.to(dev) for q in qkv_h]
+    outs = [torch.empty(N_VOX, C, dtype=dtype, device=dev) for _ in range(n_sets)]
+    geoms = [window.resolve_geometry(1, dims, WINDOW, (0, 0, 0)), window.resolve_geometry(1, dims, WINDOW, SHIFT)]
+    tile = attention.default_tile_rows(HEADS, HEAD_DIM, dtype)
+    scale = HEAD_DIM ** -0.5
+    scratch = torch.empty(1, dtype=torch.int32, device=dev)
+
+    def one_pass(i, g, q, o):
+        nonlocal scratch
+        plan = window.bucket_windows(coords=coords, geom=g, rpb_window=WINDOW, tile_rows=tile, scratch=scratch)
+        attention.window_attention_fused(q, plan, table, scale, use_mask=bool(g.shifted), out=o)
+        return plan
+
+    L = _lib.PlanLayout()
+    _lib.check(_lib.lib.ssw_plan_layout_init(L, N_VOX, geoms[0].n_windows, geoms[0].n_per_window, tile), "layout")
+    scratch = torch.empty(L.scratch_ints, dtype=torch.int32, device=dev)
+
+    def step(i):
+        s = i % n_sets
+        one_pass(i, geoms[0], qkv[s], outs[s])
+        return one_pass(i, geoms[1], qkv[s], outs[s])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        plan = step(i)
+    barrier()
+    err = plan.stats()["error"]
+    if err:
+        raise SystemExit(f"device error bits {err}")
+
+    # ---- timed region: K steps, device-timed, max over ranks --------------------------------
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            step(i)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        # keep the sampler alive over a second identical burst when the region was too short to sample
+        t_end = time.time() + 0.6
+        i = 0
+        while time.time() < t_end and len(clk.rows) < 3:
+            step(i)
+            i += 1
+        torch.cuda.synchronize()
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    value = 2.0 * N_VOX * world * args.steps / (ms * 1e-3)
+
+    # ---- dominant kernel alone: k_attn_fused, CUDA events around each launch ----------------
+    plans = [window.bucket_windows(coords=coords, geom=g, rpb_window=WINDOW, tile_rows=tile) for g in geoms]
+    torch.cuda.synchronize()
+    reps = max(10, min(50, args.steps * 2))
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for i in range(reps):
+        s = i % n_sets
+        evs[i][0].record()
+        attention.window_attention_fused(qkv[s], plans[i % 2], table, scale, use_mask=bool(i % 2), out=outs[s])
+        evs[i][1].record()
+    torch.cuda.synchronize()
+    k_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    bevs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for i in range(reps):
+        bevs[i][0].record()
+        window.bucket_windows(coords=coords, geom=geoms[i % 2], rpb_window=WINDOW, tile_rows=tile, scratch=scratch)
+        bevs[i][1].record()
+    torch.cuda.synchronize()
+    b_ms = statistics.mean(a.elapsed_time(b) for a, b in bevs)
+    peak, peak_src = measured_peak_gbs()
+    alg_bytes = algorithmic_bytes_per_voxel(elt) * N_VOX
+    achieved = alg_bytes / (k_ms * 1e-3) / 1e9
+
+    # ---- end to end: host buffers in, host result out, through the public Python API ---------
+    out_h = [torch.empty(N_VOX, C, dtype=dtype).pin_memory() for _ in range(n_sets)]
+
+    def e2e_step(i):
+        s = i % n_sets
+        c_d = coords_h.to(dev, non_blocking=True)
+        q_d = qkv_h[s].to(dev, non_blocking=True)
+        for g in geoms:
+            plan = window.bucket_windows(coords=c_d, geom=g, rpb_window=WINDOW, tile_rows=tile, scratch=scratch)
+            o = attention.window_attention_fused(q_d, plan, table, scale, use_mask=bool(g.shifted), out=outs[s])
+            out_h[s].copy_(o, non_blocking=True)
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    k_e2e = max(3, min(args.steps, 20))
+    e0.record()
+    for i in range(k_e2e):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = 2.0 * N_VOX * world * k_e2e / (float(t.item()) * 1e-3)
+    h2d = coords_h.numel() * 4 + qkv_h[0].numel() * elt
+    d2h = 2 * N_VOX * C * elt
+
+    st = plans[0].stats()
+    res = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": args.dtype, "data": "synthetic",
+        "config": {"workload": "configs[1]: W-MSA + SW-MSA(shift 3, masked) on one synthetic 8x8x3 m room at 2 cm, "
+                               f"{N_VOX} voxels per GPU, C=96, 3 heads x 32, window 7^3, bucketing + fused attention core "
+                               "(qkv resident in HBM)",
+                   "voxels_per_step_per_gpu": 2 * N_VOX, "windows": st["windows"], "sum_c2": st["sum_c2"],
+                   "c_max": st["c_max"], "tile_rows": tile,
+                   "l2": f"inputs {alg_bytes/1e6:.0f} MB per pass, {n_sets} rotating qkv/out sets ({n_sets*alg_bytes/1e6:.0f} MB) > 126 MB L2",
+                   "parallelism": f"scene per GPU x{world}"},
+        "clocks": clk.summary(),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": k_e2e},
+        "gpu_launches": KERNELS_PER_PASS * 2 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "k_attn_fused", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES[args.dtype],
+                     "algorithmic_bytes": alg_bytes, "kernel_ms": k_ms, "bucketing_ms": b_ms},
+    }
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            res["cpu_baseline"] = cpu_baseline(seconds=args.cpu_seconds)
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs: the oracle (a PyTorch CPU restatement of upstream; upstream itself has no CPU path)
+# ------------------------------------------------------------------------------------------------
+def _cpu_sample(seed: int = 0, crop: int = 200):
+    """A bounded sample of the workload: the x,y < `crop` corner of the room (about a quarter of the
+    voxels), small enough for upstream's int32 index hash (B_w*H*n*hd < 2^31) to be valid."""
+    from sparseswin3d_b200 import scenes
+
+    coords, dims = scenes.room_scene(N_VOX, seed=seed)
+    keep = (coords[:, 1] < crop) & (coords[:, 2] < crop)
+    c = torch.from_numpy(coords[keep].copy())
+    g = torch.Generator().manual_seed(1000 + seed)
+    qkv = torch.randn(c.shape[0], 3, HEADS, HEAD_DIM, generator=g)
+    table = torch.randn((2 * WINDOW[0] - 1) ** 3, HEADS, generator=g) * 0.02
+    return c, (crop, crop, dims[2]), qkv, table
+
+
+def _cpu_step(O, c, dims, qkv, table, rpi):
+    for shift in ((0, 0, 0), SHIFT):
+        idx, Bw, n, ws, ss, dp = O.window_keys(c, 1, dims, WINDOW, shift)
+        mask = O.compute_mask(dp, ws, ss) if any(ss) else None
+        O.window_attention_core(qkv, idx, Bw, n, HEAD_DIM ** -0.5, table, rpi, mask)
+
+
+def cpu_baseline(seconds: float = 15.0):
+    from oracle import ssw_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    c, dims, qkv, table = _cpu_sample()
+    rpi = O.relative_position_index(WINDOW)
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        _cpu_step(O, c, dims, qkv, table, rpi)
+        n += 1
+        if time.perf_counter() - t0 > seconds or n >= 5:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * c.shape[0] * n / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n} step(s) of W-MSA+SW-MSA on the x,y<200 corner of the scene ({c.shape[0]} voxels, fp32), "
+                      "oracle/ssw_oracle.py on torch CPU"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    from oracle import ssw_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    c, dims, qkv, table = _cpu_sample()
+    rpi = O.relative_position_index(WINDOW)
+    steps = max(1, min(args.steps, 5))
+    warm = 1
+    for _ in range(warm):
+        _cpu_step(O, c, dims, qkv, table, rpi)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        _cpu_step(O, c, dims, qkv, table, rpi)
+    dt = time.perf_counter() - t0
+    v = 2.0 * c.shape[0] * steps / dt
+    sample = (f"each step = W-MSA+SW-MSA on the x,y<200 corner of the scene ({c.shape[0]} voxels, fp32); upstream has no "
+              "CPU path and its CUDA extension needs a GPU, so this is oracle/ssw_oracle.py (a PyTorch CPU restatement)")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[1] (bounded sample): W-MSA + SW-MSA on a synthetic room, C=96, 3 heads x 32, "
+                               "window 7^3", "voxels_per_step": 2 * c.shape[0]},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
