@@ -140,7 +140,7 @@ def run_ours(args):
     qkv = [q.to(dev) for q in qkv_h]
     outs = [torch.empty(N_VOX, C, dtype=dtype, device=dev) for _ in range(n_sets)]
     geoms = [window.resolve_geometry(1, dims, WINDOW, (0, 0, 0)), window.resolve_geometry(1, dims, WINDOW, SHIFT)]
-    tile = attention.default_tile_rows(HEADS, HEAD_DIM, dtype)
+    tile = attention.default_tile_rows(HEADS, HEAD_DIM, dtype, WINDOW)
     scale = HEAD_DIM ** -0.5
     scratch = torch.empty(1, dtype=torch.int32, device=dev)
 
@@ -154,16 +154,17 @@ def run_ours(args):
     _lib.check(_lib.lib.ssw_plan_layout_init(L, N_VOX, geoms[0].n_windows, geoms[0].n_per_window, tile), "layout")
     scratch = torch.empty(L.scratch_ints, dtype=torch.int32, device=dev)
 
-    def step(i):
-        s = i % n_sets
-        one_pass(i, geoms[0], qkv[s], outs[s])
-        return one_pass(i, geoms[1], qkv[s], outs[s])
+    def step(s):
+        s = s % n_sets
+        one_pass(s, geoms[0], qkv[s], outs[s])
+        return one_pass(s, geoms[1], qkv[s], outs[s])
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    # Eager warm-up (also builds every lazily initialised CUDA object before capture).
     for i in range(max(args.warmup, 3)):
         plan = step(i)
     barrier()
@@ -171,21 +172,42 @@ def run_ours(args):
     if err:
         raise SystemExit(f"device error bits {err}")
 
+    # The host side is Python: one step is ~20 launches, and enqueueing them from the interpreter
+    # is slower than the GPU runs them.  The product path for repeated steps is therefore a CUDA
+    # graph per step (captured once, replayed): capture one step per rotating buffer set.
+    side = torch.cuda.Stream(device=dev)
+
+    def capture(fn, n):
+        graphs = []
+        with torch.cuda.stream(side):
+            for s in range(n):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    fn(s)
+                graphs.append(g)
+        torch.cuda.synchronize()
+        return graphs
+
+    step_graphs = capture(step, n_sets)
+    for i in range(max(args.warmup, 3)):
+        step_graphs[i % n_sets].replay()
+    barrier()
+
     # ---- timed region: K steps, device-timed, max over ranks --------------------------------
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
         barrier()
         e0.record()
         for i in range(args.steps):
-            step(i)
+            step_graphs[i % n_sets].replay()
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
-        # keep the sampler alive over a second identical burst when the region was too short to sample
+        # keep the sampler alive over identical work when the region was too short to sample
         t_end = time.time() + 0.6
         i = 0
         while time.time() < t_end and len(clk.rows) < 3:
-            step(i)
+            step_graphs[i % n_sets].replay()
             i += 1
         torch.cuda.synchronize()
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -194,48 +216,62 @@ def run_ours(args):
     ms = float(t.item())
     value = 2.0 * N_VOX * world * args.steps / (ms * 1e-3)
 
-    # ---- dominant kernel alone: k_attn_fused, CUDA events around each launch ----------------
+    # ---- dominant kernel alone: graphs of `reps` back-to-back k_attn_fused launches ----------
     plans = [window.bucket_windows(coords=coords, geom=g, rpb_window=WINDOW, tile_rows=tile) for g in geoms]
     torch.cuda.synchronize()
-    reps = max(10, min(50, args.steps * 2))
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
-    for i in range(reps):
-        s = i % n_sets
-        evs[i][0].record()
-        attention.window_attention_fused(qkv[s], plans[i % 2], table, scale, use_mask=bool(i % 2), out=outs[s])
-        evs[i][1].record()
-    torch.cuda.synchronize()
-    k_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
-    bevs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
-    for i in range(reps):
-        bevs[i][0].record()
-        window.bucket_windows(coords=coords, geom=geoms[i % 2], rpb_window=WINDOW, tile_rows=tile, scratch=scratch)
-        bevs[i][1].record()
-    torch.cuda.synchronize()
-    b_ms = statistics.mean(a.elapsed_time(b) for a, b in bevs)
+    reps = 12
+
+    def attn_only(_):
+        for i in range(reps):
+            s = i % n_sets
+            attention.window_attention_fused(qkv[s], plans[i % 2], table, scale, use_mask=bool(i % 2), out=outs[s])
+
+    def bucket_only(_):
+        for i in range(reps):
+            window.bucket_windows(coords=coords, geom=geoms[i % 2], rpb_window=WINDOW, tile_rows=tile, scratch=scratch)
+
+    def time_graph(fn):
+        g = capture(fn, 1)[0]
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) / reps)
+        return statistics.median(times)
+
+    k_ms = time_graph(attn_only)
+    b_ms = time_graph(bucket_only)
     peak, peak_src = measured_peak_gbs()
     alg_bytes = algorithmic_bytes_per_voxel(elt) * N_VOX
     achieved = alg_bytes / (k_ms * 1e-3) / 1e9
 
     # ---- end to end: host buffers in, host result out, through the public Python API ---------
     out_h = [torch.empty(N_VOX, C, dtype=dtype).pin_memory() for _ in range(n_sets)]
+    c_d = torch.empty_like(coords)
+    q_d = torch.empty_like(qkv[0])
 
-    def e2e_step(i):
-        s = i % n_sets
-        c_d = coords_h.to(dev, non_blocking=True)
-        q_d = qkv_h[s].to(dev, non_blocking=True)
+    def e2e_step(s):
+        c_d.copy_(coords_h, non_blocking=True)
+        q_d.copy_(qkv_h[s], non_blocking=True)
         for g in geoms:
             plan = window.bucket_windows(coords=c_d, geom=g, rpb_window=WINDOW, tile_rows=tile, scratch=scratch)
             o = attention.window_attention_fused(q_d, plan, table, scale, use_mask=bool(g.shifted), out=outs[s])
             out_h[s].copy_(o, non_blocking=True)
 
+    e2e_graphs = capture(e2e_step, n_sets)
     for i in range(3):
-        e2e_step(i)
+        e2e_graphs[i % n_sets].replay()
     barrier()
     k_e2e = max(3, min(args.steps, 20))
     e0.record()
     for i in range(k_e2e):
-        e2e_step(i)
+        e2e_graphs[i % n_sets].replay()
     e1.record()
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
@@ -256,14 +292,15 @@ def run_ours(args):
                    "voxels_per_step_per_gpu": 2 * N_VOX, "windows": st["windows"], "sum_c2": st["sum_c2"],
                    "c_max": st["c_max"], "tile_rows": tile,
                    "l2": f"inputs {alg_bytes/1e6:.0f} MB per pass, {n_sets} rotating qkv/out sets ({n_sets*alg_bytes/1e6:.0f} MB) > 126 MB L2",
-                   "parallelism": f"scene per GPU x{world}"},
+                   "parallelism": f"scene per GPU x{world}", "launch": "one CUDA graph replay per step"},
         "clocks": clk.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": k_e2e},
         "gpu_launches": KERNELS_PER_PASS * 2 * args.steps,
         "roofline": {"bound": "hbm", "kernel": "k_attn_fused", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES[args.dtype],
-                     "algorithmic_bytes": alg_bytes, "kernel_ms": k_ms, "bucketing_ms": b_ms},
+                     "algorithmic_bytes": alg_bytes, "kernel_ms": k_ms, "bucketing_ms": b_ms,
+                     "timing": "CUDA events around a replayed CUDA graph of 12 back-to-back launches, median of 5"},
     }
     if world > 1:
         dist.barrier()

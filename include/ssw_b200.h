@@ -92,7 +92,8 @@ enum {
   SSW_H_SUMC2_HI = 6,
   SSW_H_TILE = 7,     /* tile_rows the plan was built for                              */
   SSW_H_TICKET_A = 8, /* internal                                                      */
-  SSW_H_TICKET_B = 9  /* internal                                                      */
+  SSW_H_TICKET_B = 9, /* internal                                                      */
+  SSW_H_PACKS_SMALL = 10 /* leading work items that are packs of windows with c <= tile */
 };
 
 typedef struct ssw_plan_layout {
@@ -124,11 +125,12 @@ typedef struct ssw_plan_layout {
   int64_t scratch_ints;
 } ssw_plan_layout;
 
-/* Host only.  tile_rows = 0 picks the default for (heads, channels, dtype). */
+/* Host only.  tile_rows in 1..64; 0 means 64. */
 int ssw_plan_layout_init(ssw_plan_layout* L, int64_t n_vox, int32_t n_windows, int32_t n_per_window,
                          int32_t tile_rows);
-/* The default tile_rows for a configuration (host only). */
-int32_t ssw_default_tile_rows(int32_t heads, int32_t head_dim, int dtype);
+/* The default tile_rows for a configuration (host only): the largest tile whose two pipeline
+ * stages, plus the bias table when it is small enough to stage, let two CTAs share an SM. */
+int32_t ssw_default_tile_rows(int32_t heads, int32_t head_dim, int dtype, const int32_t rpb_window[3]);
 
 /* Key source of ssw_bucket_windows: exactly one of `coords` (with `geom`) or `indices` is
  * non-NULL.  With `indices` ([N,2] int32, the layout window_partition_sparse leaves in

@@ -53,7 +53,7 @@ def _load() -> C.CDLL:
         "ssw_version": (C.c_int, []),
         "ssw_geometry_resolve": (C.c_int, [P(Geometry)]),
         "ssw_window_keys": (C.c_int, [vp, i64, P(Geometry), vp, vp, vp, vp]),
-        "ssw_default_tile_rows": (i32, [i32, i32, C.c_int]),
+        "ssw_default_tile_rows": (i32, [i32, i32, C.c_int, P(i32)]),
         "ssw_plan_layout_init": (C.c_int, [P(PlanLayout), i64, i32, i32, i32]),
         "ssw_bucket_windows": (C.c_int, [vp, P(Geometry), vp, vp, i32, P(i32), P(PlanLayout), vp, vp, vp]),
         "ssw_attn_fused": (C.c_int, [vp, C.c_int, i32, i32, P(PlanLayout), vp, vp, P(i32), f32, C.c_int, vp, vp, vp]),

@@ -12,8 +12,10 @@ from ._lib import check, dtype_code, lib, ptr, stream_ptr
 from .window import WindowPlan, bucket_windows
 
 
-def default_tile_rows(num_heads: int, head_dim: int, dtype: torch.dtype) -> int:
-    return int(lib.ssw_default_tile_rows(num_heads, head_dim, dtype_code(dtype)))
+def default_tile_rows(num_heads: int, head_dim: int, dtype: torch.dtype, rpb_window: Sequence[int] = (7, 7, 7)) -> int:
+    """Rows per work item the fused kernel wants for this configuration (pass it to bucket_windows)."""
+    rw = (_lib.i32 * 3)(*[int(x) for x in rpb_window])
+    return int(lib.ssw_default_tile_rows(num_heads, head_dim, dtype_code(dtype), rw))
 
 
 def window_attention_fused(qkv: torch.Tensor, plan: WindowPlan, table: torch.Tensor, scale: float,
@@ -96,7 +98,7 @@ class WindowAttentionSparse(nn.Module):
         nn.init.trunc_normal_(self.relative_position_bias_table, std=0.02, a=-2.0, b=2.0)
 
     def tile_rows(self, dtype: torch.dtype) -> int:
-        return default_tile_rows(self.num_heads, self.dim // self.num_heads, dtype)
+        return default_tile_rows(self.num_heads, self.dim // self.num_heads, dtype, self.window_size)
 
     def plan(self, x, mask: Optional[torch.Tensor], dtype: torch.dtype) -> WindowPlan:
         return bucket_windows(indices=x.indices, n_windows=int(x.batch_size), n_per_window=int(x.spatial_shape[0]),

@@ -1,13 +1,27 @@
 // Fused window attention for sparse voxel windows: QK^T, relative-position bias, shift mask,
 // row softmax (upstream semantics: max starts at 0, denominator + 1e-8) and P.V in one kernel.
 //
-// CUDA-core path.  One CTA = one work item of the plan: either a *pack* of several windows that
-// all hold exactly c voxels (c <= tile), or one tile of query rows of a window with c > tile.
-// Thread (h, r) owns query row r of head h: its q row lives in registers, the K|V halves of the
-// item's voxel rows are gathered into shared memory with one 1-D bulk (TMA) copy per voxel
-// (2*C contiguous elements: k and v sit side by side in the qkv row), and the thread walks the
-// keys of its own window with a chunked online softmax.  Scores are accumulated as a sequential
-// FMA chain over the head channels, the order upstream's kernel uses (ops.cu:371-375).
+// CUDA-core path, one persistent CTA per SM, software-pipelined.  The plan's work items are
+// either *packs* of windows that all hold exactly c voxels (c <= tile) or query tiles of a window
+// with c > tile.
+//
+// Phase A (packs).  CTA b owns items b, b+grid, ...; item i uses pipeline stage i % S and is
+// computed by consumer group i % G.  One producer warp runs ahead: it reads the item descriptor
+// and the voxel ids of the item's rows and gathers the whole q|k|v rows (3*C contiguous elements
+// each) into the stage with one 1-D bulk (TMA) copy per voxel, completing on the stage's `full`
+// mbarrier.  The bias table lives in shared memory.  In a consumer group, thread (hg, r) owns
+// query row r for heads hg, hg+HG, ...: q comes from the staged row, the thread walks the keys of
+// its own window with a chunked online softmax in the log2 domain (dot products and the P.V
+// update are packed fp32 FMAs, fma.rn.f32x2), and writes its output slice back into the stage.
+// When the group is done, its first warp streams the finished rows to global memory with bulk
+// (TMA) stores and hands the stage back through `empty`.  16-bit inputs are copied into the upper
+// half of each fp32 row and widened in place once per item.
+//
+// Phase B (windows with c > tile): the same arithmetic, one query tile per item, key tiles
+// streamed through stage 0 without overlap; q and the output go straight through global memory.
+//
+// Every wait is a bounded poll of an mbarrier; on expiry the kernel sets SSW_DEV_TIMEOUT in the
+// plan header and every thread leaves through the same exit.
 #include <math.h>
 
 #include <type_traits>
@@ -15,6 +29,10 @@
 #include "ssw_common.cuh"
 
 namespace ssw {
+
+constexpr int kMaxStages = 6;
+constexpr int kMaxGroups = 4;
+constexpr int kMaxTile = 64;
 
 struct AttnParams {
   const void* qkv;
@@ -28,277 +46,644 @@ struct AttnParams {
   const int32_t* coo_start;
   const float* table;
   int rel_off;
-  int H, C, tile;
+  int H, C, tile, HG;
+  int group_threads;  // threads of one consumer group (multiple of 32) = ceil32(tile * HG)
+  int groups, stages;
   float scale;
   int use_mask;
-  int row_stride;  // bytes between staged K|V rows in shared memory
+  int row_stride;     // bytes between fp32 rows in a stage
+  int stage_bytes;    // bytes of one pipeline stage
+  int out_off;        // byte offset of the 16-bit output staging area inside a stage (0 for fp32)
+  int table_floats;   // > 0: the bias table is staged in shared memory (that many floats)
 };
 
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kKeyChunk = 4;
+
+// Shared memory: [barriers 256 B][bias table][stage 0][stage 1]...
+// Stage: [desc int4][vox int[kMaxTile]][kmeta int2[kMaxTile]][rows tile*row_stride][16-bit out staging]
+constexpr int kBarBytes = 256;
+constexpr int kStageVoxOff = 16;
+constexpr int kStageMetaOff = kStageVoxOff + kMaxTile * 4;
+constexpr int kStageRowsOff = kStageMetaOff + kMaxTile * 8;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// shared -> global bulk (TMA) store of `bytes` (multiple of 16, both addresses 16-byte aligned)
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// make generic-proxy writes to shared memory visible to the async proxy (bulk stores)
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Barrier among the warps of one consumer group, built on an mbarrier so that the wait is bounded.
+__device__ __forceinline__ bool group_barrier(uint64_t* bar, uint32_t& phase, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+  const bool ok = mbar_wait_bounded(bar, phase);
+  phase ^= 1;
+  return ok;
+}
+
 template <typename T>
-struct Elt;
+__device__ __forceinline__ void widen8(const uint4& u, float4& a, float4& b);
 template <>
-struct Elt<float> {
-  static constexpr int kVec = 4;  // elements per 16-byte vector
-  __device__ static void unpack(const uint4& u, float* f) {
-    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y);
-    f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
-  }
-  __device__ static uint4 pack(const float* f) {
-    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
-  }
-  __device__ static float round_trip(float x) { return x; }
-};
+__device__ __forceinline__ void widen8<__nv_bfloat16>(const uint4& u, float4& a, float4& b) {
+  a = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                  __uint_as_float(u.y & 0xffff0000u));
+  b = make_float4(__uint_as_float(u.z << 16), __uint_as_float(u.z & 0xffff0000u), __uint_as_float(u.w << 16),
+                  __uint_as_float(u.w & 0xffff0000u));
+}
 template <>
-struct Elt<__nv_bfloat16> {
-  static constexpr int kVec = 8;
-  __device__ static void unpack(const uint4& u, float* f) {
-    f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
-    f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
-    f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
-    f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
-  }
-  __device__ static uint32_t pk(float a, float b) {
+__device__ __forceinline__ void widen8<__half>(const uint4& u, float4& a, float4& b) {
+  float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+  float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+  float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&u.z));
+  float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&u.w));
+  a = make_float4(p0.x, p0.y, p1.x, p1.y);
+  b = make_float4(p2.x, p2.y, p3.x, p3.y);
+}
+template <>
+__device__ __forceinline__ void widen8<float>(const uint4&, float4&, float4&) {}
+
+template <typename T>
+__device__ __forceinline__ T from_float(float f);
+template <>
+__device__ __forceinline__ float from_float<float>(float f) { return f; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float f) { return __float2bfloat16_rn(f); }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float f) { return __float2half_rn(f); }
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&v);
-  }
-  __device__ static uint4 pack(const float* f) {
-    return make_uint4(pk(f[0], f[1]), pk(f[2], f[3]), pk(f[4], f[5]), pk(f[6], f[7]));
-  }
-  __device__ static float round_trip(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-};
-template <>
-struct Elt<__half> {
-  static constexpr int kVec = 8;
-  __device__ static void up(uint32_t w, float* f) {
-    __half2 h = *reinterpret_cast<__half2*>(&w);
-    float2 v = __half22float2(h);
-    f[0] = v.x; f[1] = v.y;
-  }
-  __device__ static void unpack(const uint4& u, float* f) {
-    up(u.x, f); up(u.y, f + 2); up(u.z, f + 4); up(u.w, f + 6);
-  }
-  __device__ static uint32_t pk(float a, float b) {
+  } else {
     __half2 v = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&v);
   }
-  __device__ static uint4 pack(const float* f) {
-    return make_uint4(pk(f[0], f[1]), pk(f[2], f[3]), pk(f[4], f[5]), pk(f[6], f[7]));
+}
+
+// Online-softmax state of one (query row, head).
+template <int HD>
+struct RowState {
+  float2 q[HD / 2];
+  float2 acc[HD / 2];
+  float m, l;
+  __device__ __forceinline__ void reset() {
+#pragma unroll
+    for (int e = 0; e < HD / 2; ++e) acc[e] = make_float2(0.f, 0.f);
+    m = 0.f;  // upstream's row maximum starts from 0 (ops.cu:137)
+    l = 0.f;
   }
-  __device__ static float round_trip(float x) { return __half2float(__float2half_rn(x)); }
 };
 
-constexpr int kKeyChunk = 4;
-
+// q row of one head from global memory -> fp32 pairs scaled by `scale`.
 template <typename T, int HD>
-__device__ __forceinline__ float dot_row(const float (&q)[HD], const unsigned char* krow) {
-  constexpr int V = Elt<T>::kVec;
-  float s = 0.f;
+__device__ __forceinline__ void load_q_global(const T* src, float scale, float2 (&q)[HD / 2]) {
+  if constexpr (sizeof(T) == 4) {
 #pragma unroll
-  for (int d = 0; d < HD; d += V) {
-    uint4 u = *reinterpret_cast<const uint4*>(krow + d * sizeof(T));
-    float f[V];
-    Elt<T>::unpack(u, f);
+    for (int e = 0; e < HD / 4; ++e) {
+      float4 v = __ldg(reinterpret_cast<const float4*>(src) + e);
+      q[2 * e] = make_float2(v.x * scale, v.y * scale);
+      q[2 * e + 1] = make_float2(v.z * scale, v.w * scale);
+    }
+  } else {
 #pragma unroll
-    for (int e = 0; e < V; ++e) s = fmaf(q[d + e], f[e], s);
+    for (int e = 0; e < HD / 8; ++e) {
+      uint4 u = __ldg(reinterpret_cast<const uint4*>(src) + e);
+      float4 a, b;
+      widen8<T>(u, a, b);
+      q[4 * e] = make_float2(a.x * scale, a.y * scale);
+      q[4 * e + 1] = make_float2(a.z * scale, a.w * scale);
+      q[4 * e + 2] = make_float2(b.x * scale, b.y * scale);
+      q[4 * e + 3] = make_float2(b.z * scale, b.w * scale);
+    }
   }
+}
+template <int HD>
+__device__ __forceinline__ void load_q_smem(const float4* src, float scale, float2 (&q)[HD / 2]) {
+#pragma unroll
+  for (int e = 0; e < HD / 4; ++e) {
+    const float4 v = src[e];
+    q[2 * e] = make_float2(v.x * scale, v.y * scale);
+    q[2 * e + 1] = make_float2(v.z * scale, v.w * scale);
+  }
+}
+
+// In-place widening of `n_rows` staged 16-bit rows (each copied to byte offset row_elems*2 of its
+// fp32 row) by `n_thr` cooperating threads.  Chunks are handled in ascending order, eight per
+// thread per round, reads before writes: a float write only ever lands on sources of the same or
+// an earlier chunk.  `sync` separates the reads from the writes; returns false if it timed out.
+template <typename T, typename Sync>
+__device__ __forceinline__ bool widen_rows(unsigned char* rows, int row_stride, int row_elems, int n_rows, int tid,
+                                           int n_thr, Sync sync) {
+  bool ok = true;
+  if constexpr (sizeof(T) == 2) {
+    const int cpr = row_elems / 8;  // 16-byte chunks per row
+    const int total = n_rows * cpr;
+    for (int base = 0; base < total; base += n_thr * 8) {
+      uint4 u[8];
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        const int ci = base + x * n_thr + tid;
+        if (ci < total) {
+          const int rr = ci / cpr, cc = ci - rr * cpr;
+          u[x] = *reinterpret_cast<const uint4*>(rows + (size_t)rr * row_stride + row_elems * 2 + cc * 16);
+        }
+      }
+      ok = sync() && ok;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        const int ci = base + x * n_thr + tid;
+        if (ci < total) {
+          const int rr = ci / cpr, cc = ci - rr * cpr;
+          float4 a, b;
+          widen8<T>(u[x], a, b);
+          float4* dst = reinterpret_cast<float4*>(rows + (size_t)rr * row_stride + cc * 32);
+          dst[0] = a;
+          dst[1] = b;
+        }
+      }
+      ok = sync() && ok;
+    }
+  }
+  return ok;
+}
+
+// Keys [jb, je) of my window, staged at `rows` (row index = key - k0).  `k_off` is the byte offset
+// of this head's k slice inside a row; v sits C floats further.  kEmit: second pass that writes
+// the normalised probabilities instead of accumulating.
+template <typename T, int HD, bool kEmit, bool kTableSmem>
+__device__ __forceinline__ void attend_keys(RowState<HD>& st, const unsigned char* rows, const int2* kmeta,
+                                            int row_stride, int k0, int jb, int je, int k_off, int C,
+                                            const float* table_h, bool use_mask, int my_region, float inv_l,
+                                            T* emit_dst) {
+  const float mask_add = -100.0f * kLog2e;
+  for (int j = jb; j < je; j += kKeyChunk) {
+    float s[kKeyChunk];
+    const unsigned char* rowp[kKeyChunk];
+#pragma unroll
+    for (int u = 0; u < kKeyChunk; ++u) {
+      const int jj = min(j + u, je - 1) - k0;
+      rowp[u] = rows + (size_t)jj * row_stride + k_off;
+      const float4* kr = reinterpret_cast<const float4*>(rowp[u]);
+      // two independent partial sums per key keep the FMA dependency chains short
+      float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int e = 0; e < HD / 4; ++e) {
+        const float4 kv = kr[e];
+        sa = __ffma2_rn(st.q[2 * e], make_float2(kv.x, kv.y), sa);
+        sb = __ffma2_rn(st.q[2 * e + 1], make_float2(kv.z, kv.w), sb);
+      }
+      const int2 km = kmeta[jj];
+      const float bias = kTableSmem ? *(table_h - km.x) : __ldg(table_h - km.x);
+      float sc = (((sa.x + sb.x) + (sa.y + sb.y)) + bias) * kLog2e;
+      if (use_mask && my_region != (km.y & 31)) sc += mask_add;
+      s[u] = (j + u < je) ? sc : -INFINITY;
+    }
+    if constexpr (!kEmit) {
+      float mc = s[0];
+#pragma unroll
+      for (int u = 1; u < kKeyChunk; ++u) mc = fmaxf(mc, s[u]);
+      if (mc > st.m) {
+        const float corr = fast_exp2(st.m - mc);
+        st.l *= corr;
+        const float2 c2 = make_float2(corr, corr);
+#pragma unroll
+        for (int e = 0; e < HD / 2; ++e) st.acc[e] = __fmul2_rn(st.acc[e], c2);
+        st.m = mc;
+      }
+#pragma unroll
+      for (int u = 0; u < kKeyChunk; ++u) {
+        const float pu = fast_exp2(s[u] - st.m);
+        st.l += pu;
+        const float2 p2 = make_float2(pu, pu);
+        const float4* vr = reinterpret_cast<const float4*>(rowp[u] + C * 4);
+#pragma unroll
+        for (int e = 0; e < HD / 4; ++e) {
+          const float4 vv = vr[e];
+          st.acc[2 * e] = __ffma2_rn(p2, make_float2(vv.x, vv.y), st.acc[2 * e]);
+          st.acc[2 * e + 1] = __ffma2_rn(p2, make_float2(vv.z, vv.w), st.acc[2 * e + 1]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < kKeyChunk; ++u)
+        if (j + u < je) emit_dst[j - jb + u] = from_float<T>(fast_exp2(s[u] - st.m) * inv_l);
+    }
+  }
+}
+
+// acc * inv_l as T, 16-byte vector stores (global or shared destination)
+template <typename T, int HD>
+__device__ __forceinline__ void store_out(T* dst, const RowState<HD>& st, float inv_l) {
+  const float2 i2 = make_float2(inv_l, inv_l);
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int e = 0; e < HD / 4; ++e) {
+      const float2 a = __fmul2_rn(st.acc[2 * e], i2), b = __fmul2_rn(st.acc[2 * e + 1], i2);
+      reinterpret_cast<float4*>(dst)[e] = make_float4(a.x, a.y, b.x, b.y);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < HD / 8; ++e) {
+      uint32_t w[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float2 a = __fmul2_rn(st.acc[4 * e + x], i2);
+        w[x] = pack2<T>(a.x, a.y);
+      }
+      reinterpret_cast<uint4*>(dst)[e] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+template <typename T, int HD, bool kTableSmem, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  constexpr bool kHalf = sizeof(T) == 2;
+  const int tile = p.tile, C = p.C, H = p.H;
+  const int S = p.stages, G = p.groups;
+  const int n_small = p.header[SSW_H_PACKS_SMALL];
+  const int n_items = p.header[SSW_H_PACKS];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);   // [kMaxStages] data landed
+  uint64_t* empty = full + kMaxStages;                   // [kMaxStages] stage may be refilled
+  uint64_t* done = empty + kMaxStages;                   // [kMaxStages] group finished computing
+  uint64_t* gbar = done + kMaxStages;                    // [kMaxGroups] group-internal barrier
+  uint64_t* bbar = gbar + kMaxGroups;                    // phase B copies
+  float* table_s = reinterpret_cast<float*>(smem + kBarBytes);
+  unsigned char* stage0 = smem + kBarBytes + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
+  const float* table_base = kTableSmem ? table_s : p.table;
+  const int gsize = p.group_threads;
+  const int gwarps = gsize >> 5;
+  const int n_cons = gsize * G;
+  const bool is_producer = (int)threadIdx.x >= n_cons;
+  const int lane = threadIdx.x & 31;
+  const int row_elems = 3 * C;  // q|k|v elements staged per voxel
+  const uint32_t copy_bytes = row_elems * sizeof(T);
+  const int copy_off = kHalf ? row_elems * 2 : 0;  // 16-bit rows land in the upper half of the fp32 row
+  const uint32_t out_bytes = C * sizeof(T);
+  const int n_hiter = H / p.HG;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+      mbar_init(done + s, gwarps);
+    }
+    for (int g = 0; g < G; ++g) mbar_init(gbar + g, gwarps);
+    mbar_init(bbar, 1);
+    mbar_fence_init();
+  }
+  if constexpr (kTableSmem)
+    for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) table_s[i] = __ldg(p.table + i);
+  __syncthreads();
+
+  // ------------------------------------------------------------------------------------------
+  // Phase A: packs, producer / consumer pipeline
+  // ------------------------------------------------------------------------------------------
+  const int my_items = n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  bool timed_out = false;
+  if (is_producer) {
+    // register pipeline: descriptor of item i+1, voxel ids / metadata of item i
+    int4 d_cur = make_int4(0, 0, 0, 0), d_nxt = make_int4(0, 0, 0, 0);
+    int vox[2] = {0, 0}, km[2] = {0, 0};
+    if (my_items > 0) d_cur = __ldg(p.pack_desc + blockIdx.x);
+    if (my_items > 1) d_nxt = __ldg(p.pack_desc + blockIdx.x + gridDim.x);
+    if (my_items > 0) {
+      const int nr = d_cur.z * d_cur.y;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int rr = lane + 32 * k;
+        if (rr < nr) {
+          vox[k] = __ldg(p.pack_perm + d_cur.x + rr);
+          km[k] = __ldg(p.pack_meta + d_cur.x + rr);
+        }
+      }
+    }
+    for (int i = 0; i < my_items; ++i) {
+      const int s = i % S;
+      const int use = i / S;
+      // prefetch for later iterations (nothing in this iteration waits on these loads)
+      int4 d_nn = make_int4(0, 0, 0, 0);
+      if (i + 2 < my_items) d_nn = __ldg(p.pack_desc + blockIdx.x + (size_t)(i + 2) * gridDim.x);
+      int vox_n[2] = {0, 0}, km_n[2] = {0, 0};
+      if (i + 1 < my_items) {
+        const int nr = d_nxt.z * d_nxt.y;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int rr = lane + 32 * k;
+          if (rr < nr) {
+            vox_n[k] = __ldg(p.pack_perm + d_nxt.x + rr);
+            km_n[k] = __ldg(p.pack_meta + d_nxt.x + rr);
+          }
+        }
+      }
+      if (use > 0 && !mbar_wait_bounded(empty + s, (use - 1) & 1)) {
+        timed_out = true;
+        break;
+      }
+      unsigned char* st = stage0 + (size_t)s * p.stage_bytes;
+      const int nr = d_cur.z * d_cur.y;
+      if (lane == 0) *reinterpret_cast<int4*>(st) = d_cur;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int rr = lane + 32 * k;
+        if (rr < nr) {
+          reinterpret_cast<int*>(st + kStageVoxOff)[rr] = vox[k];
+          reinterpret_cast<int2*>(st + kStageMetaOff)[rr] =
+              make_int2(meta_rel(km[k]) * H, meta_region(km[k]) | ((meta_rel(km[k]) + p.rel_off) << 8));
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_expect_tx(full + s, nr * copy_bytes);
+      __syncwarp();
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int rr = lane + 32 * k;
+        if (rr < nr)
+          bulk_g2s(st + kStageRowsOff + (size_t)rr * p.row_stride + copy_off,
+                   reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[k] * 3 * C, copy_bytes, full + s);
+      }
+      d_cur = d_nxt;
+      d_nxt = d_nn;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        vox[k] = vox_n[k];
+        km[k] = km_n[k];
+      }
+    }
+  } else {
+    const int g = threadIdx.x / gsize;
+    const int ltid = threadIdx.x - g * gsize;
+    const int hg = ltid / tile;
+    const int r = ltid - hg * tile;
+    const bool thread_used = hg < p.HG;
+    const bool store_warp = ltid < 32;
+    uint32_t gphase = 0;
+    RowState<HD> st;
+    for (int i = g; i < my_items && !timed_out; i += G) {
+      const int s = i % S;
+      const int use = i / S;
+      unsigned char* sp = stage0 + (size_t)s * p.stage_bytes;
+      unsigned char* rows = sp + kStageRowsOff;
+      const int2* kmeta = reinterpret_cast<const int2*>(sp + kStageMetaOff);
+      if (!mbar_wait_bounded(full + s, use & 1)) {
+        timed_out = true;
+        break;
+      }
+      const int4 d = *reinterpret_cast<const int4*>(sp);
+      const int c = d.y;
+      const int q_rows = d.z * c;
+      if constexpr (kHalf) {
+        if (!widen_rows<T>(rows, p.row_stride, row_elems, q_rows, ltid, gsize,
+                           [&]() { return group_barrier(gbar + g, gphase, lane); })) {
+          timed_out = true;
+          break;
+        }
+      }
+      const bool row_active = thread_used && r < q_rows;
+      const int wl = r / c;
+      const int kbeg = wl * c, kend = kbeg + c;
+      if (row_active) {
+        const int2 me = kmeta[r];
+        const int my_rel = (me.y >> 8) * H;
+        const int my_region = me.y & 31;
+        unsigned char* myrow = rows + (size_t)r * p.row_stride;
+        for (int hi = 0; hi < n_hiter; ++hi) {
+          const int h = hi * p.HG + hg;
+          load_q_smem<HD>(reinterpret_cast<const float4*>(myrow) + (h * HD) / 4, p.scale, st.q);
+          st.reset();
+          const float* table_h = table_base + my_rel + h;
+          attend_keys<T, HD, false, kTableSmem>(st, rows, kmeta, p.row_stride, 0, kbeg, kend, (C + h * HD) * 4, C,
+                                                table_h, p.use_mask != 0, my_region, 0.f, nullptr);
+          const float inv_l = 1.0f / (st.l + 1e-8f);  // ops.cu:164
+          if (p.attn_vals) {
+            const int kwin = __ldg(p.pack_win + d.w + wl);
+            T* dst = reinterpret_cast<T*>(p.attn_vals) + ((int64_t)__ldg(p.coo_start + kwin) * H + (int64_t)h * c * c) +
+                     (int64_t)(r - kbeg) * c;
+            attend_keys<T, HD, true, kTableSmem>(st, rows, kmeta, p.row_stride, 0, kbeg, kend, (C + h * HD) * 4, C,
+                                                 table_h, p.use_mask != 0, my_region, inv_l, dst);
+          }
+          // fp32: the slice that held my q; 16-bit: the stage's output area
+          T* so = kHalf ? reinterpret_cast<T*>(sp + p.out_off + (size_t)r * out_bytes) + h * HD
+                        : reinterpret_cast<T*>(myrow) + h * HD;
+          store_out<T, HD>(so, st, inv_l);
+        }
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(done + s);
+      if (store_warp) {
+        if (!mbar_wait_bounded(done + s, use & 1)) {
+          timed_out = true;
+          break;
+        }
+        const int* svox = reinterpret_cast<const int*>(sp + kStageVoxOff);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int rr = lane + 32 * k;
+          if (rr < q_rows) {
+            const unsigned char* src = kHalf ? sp + p.out_off + (size_t)rr * out_bytes : rows + (size_t)rr * p.row_stride;
+            bulk_s2g(reinterpret_cast<T*>(p.out) + (int64_t)svox[rr] * C, src, out_bytes);
+          }
+        }
+        bulk_commit();
+        bulk_wait_read_all();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+      }
+    }
+    if (store_warp) bulk_wait_all();
+  }
+  if (timed_out) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
+  // A timed-out role leaves; the other roles then time out on their own bounded waits.
+  if (__syncthreads_or(timed_out)) return;
+
+  // ------------------------------------------------------------------------------------------
+  // Phase B: windows with c > tile; one query tile per item, key tiles through stage 0
+  // ------------------------------------------------------------------------------------------
+  unsigned char* rows = stage0 + kStageRowsOff;
+  int2* kmeta = reinterpret_cast<int2*>(stage0 + kStageMetaOff);
+  uint32_t phase = 0;
+  const int hg = threadIdx.x / tile;
+  const int r = threadIdx.x - hg * tile;
+  const bool thread_used = hg < p.HG;  // the first tile*HG threads do the arithmetic
+  for (int item = n_small + blockIdx.x; item < n_items; item += gridDim.x) {
+    const int4 d = __ldg(p.pack_desc + item);
+    const int c = d.y;
+    const int q_first = (-d.z - 1) * tile;
+    const int q_rows = min(tile, c - q_first);
+    const bool row_active = thread_used && r < q_rows;
+    int my_vox = 0, my_rel = 0, my_region = 0;
+    if (row_active) {
+      const int row = d.x + q_first + r;
+      my_vox = __ldg(p.pack_perm + row);
+      const int m = __ldg(p.pack_meta + row);
+      my_rel = (meta_rel(m) + p.rel_off) * H;
+      my_region = meta_region(m);
+    }
+    const int n_tiles = (c + tile - 1) / tile;
+    const int n_pass = p.attn_vals ? 2 : 1;
+    for (int hi = 0; hi < n_hiter; ++hi) {
+      const int h = hi * p.HG + hg;
+      RowState<HD> st;
+      st.reset();
+      float inv_l = 0.f;
+      if (row_active)
+        load_q_global<T, HD>(reinterpret_cast<const T*>(p.qkv) + (int64_t)my_vox * 3 * C + h * HD, p.scale, st.q);
+      const float* table_h = table_base + my_rel + h;
+      T* emit = nullptr;
+      if (n_pass == 2 && row_active) {
+        const int kwin = __ldg(p.pack_win + d.w);
+        emit = reinterpret_cast<T*>(p.attn_vals) + ((int64_t)__ldg(p.coo_start + kwin) * H + (int64_t)h * c * c) +
+               (int64_t)(q_first + r) * c;
+      }
+      for (int pass = 0; pass < n_pass; ++pass) {
+        for (int t = 0; t < n_tiles; ++t) {
+          const int k0 = t * tile;
+          const int rows_t = min(tile, c - k0);
+          if (threadIdx.x == 0) mbar_expect_tx(bbar, rows_t * copy_bytes);
+          if ((int)threadIdx.x < rows_t) {
+            const int row = d.x + k0 + threadIdx.x;
+            const int vj = __ldg(p.pack_perm + row);
+            const int km = __ldg(p.pack_meta + row);
+            kmeta[threadIdx.x] = make_int2(meta_rel(km) * H, meta_region(km));
+            bulk_g2s(rows + (size_t)threadIdx.x * p.row_stride + copy_off,
+                     reinterpret_cast<const T*>(p.qkv) + (int64_t)vj * 3 * C, copy_bytes, bbar);
+          }
+          __syncthreads();  // kmeta visible
+          const bool ok = mbar_wait_bounded(bbar, phase);
+          if (__syncthreads_or(!ok)) {
+            if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
+            return;
+          }
+          phase ^= 1;
+          if constexpr (kHalf)
+            widen_rows<T>(rows, p.row_stride, row_elems, rows_t, threadIdx.x, blockDim.x, []() {
+              __syncthreads();
+              return true;
+            });
+          if (row_active) {
+            if (pass == 0)
+              attend_keys<T, HD, false, kTableSmem>(st, rows, kmeta, p.row_stride, k0, k0, k0 + rows_t,
+                                                    (C + h * HD) * 4, C, table_h, p.use_mask != 0, my_region, 0.f,
+                                                    nullptr);
+            else
+              attend_keys<T, HD, true, kTableSmem>(st, rows, kmeta, p.row_stride, k0, k0, k0 + rows_t,
+                                                   (C + h * HD) * 4, C, table_h, p.use_mask != 0, my_region, inv_l,
+                                                   emit + k0);
+          }
+          __syncthreads();  // everyone done with this tile before it is overwritten
+        }
+        if (pass == 0) inv_l = 1.0f / (st.l + 1e-8f);
+      }
+      if (row_active) store_out<T, HD>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD, st, inv_l);
+    }
+  }
+}
+
+// Shape of the kernel for (tile, heads, head_dim, dtype, window): heads processed in parallel (a
+// divisor of `heads`, at most 256 threads per group), pipeline stages and consumer groups that
+// fit the SM's shared memory next to the bias table (kept in shared memory when it is small: the
+// L1 that remains beside ~200 KB of stages is too small to hold it).
+constexpr int kTableSmemMax = 40 * 1024;
+constexpr size_t kSmemBudget = 226 * 1024;
+struct KernelShape {
+  int hg, group_threads, groups, stages, row_stride, stage_bytes, out_off, table_floats;
+  size_t smem;
+};
+static int table_entries(const int32_t w[3], int heads) {
+  return (2 * w[0] - 1) * (2 * w[1] - 1) * (2 * w[2] - 1) * heads;
+}
+static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, const int32_t rpb_window[3]) {
+  KernelShape s;
+  int cap = 256 / tile;
+  if (cap < 1) cap = 1;
+  s.hg = 1;
+  for (int g = 1; g <= heads && g <= cap; ++g)
+    if (heads % g == 0) s.hg = g;
+  s.group_threads = (tile * s.hg + 31) & ~31;
+  const int C = heads * head_dim;
+  s.row_stride = 3 * C * 4 + 16;  // +16 B skews rows across shared-memory banks
+  const int rows_bytes = kStageRowsOff + tile * s.row_stride;
+  s.out_off = elt == 2 ? rows_bytes : 0;
+  s.stage_bytes = rows_bytes + (elt == 2 ? tile * C * 2 : 0);
+  const int tf = table_entries(rpb_window, heads);
+  s.table_floats = tf * 4 <= kTableSmemMax ? tf : 0;
+  const size_t fixed = kBarBytes + ((s.table_floats * 4 + 15) & ~15);
+  int stages = (int)((kSmemBudget - fixed) / s.stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  s.stages = stages;
+  // one stage is always in flight; at most 1024 threads
+  int groups = stages - 1;
+  if (groups > kMaxGroups) groups = kMaxGroups;
+  while (groups > 1 && groups * s.group_threads + 32 > 1024) --groups;
+  if (groups < 1) groups = 1;
+  s.groups = groups;
+  s.smem = fixed + (size_t)(stages > 0 ? stages : 1) * s.stage_bytes;
   return s;
 }
 
-template <typename T, int HD, int MAXT, int MINB>
-__global__ void __launch_bounds__(MAXT, MINB) k_attn_fused(AttnParams p) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  const int item = blockIdx.x;
-  if (item >= p.header[SSW_H_PACKS]) return;
-  const int tile = p.tile;
-  uint64_t* bar = reinterpret_cast<uint64_t*>(smem);
-  int32_t* kmeta = reinterpret_cast<int32_t*>(smem + 16);
-  unsigned char* rows = smem + 16 + ((tile * 4 + 15) & ~15);
-
-  const int4 d = p.pack_desc[item];
-  const int c = d.y;
-  const bool big = d.z < 0;
-  const int h = threadIdx.x / tile;
-  const int r = threadIdx.x - h * tile;
-  const int q_first = big ? (-d.z - 1) * tile : 0;
-  const int q_rows = big ? min(tile, c - q_first) : d.z * c;
-  const int keys_total = big ? c : q_rows;
-  const bool active = r < q_rows;
-  const int wl = big ? 0 : r / c;                  // window inside the pack
-  const int kbeg = big ? 0 : wl * c;               // my window's keys, relative to row d.x
-  const int kend = kbeg + c;
-  const int C = p.C, H = p.H;
-  const uint32_t row_bytes = 2u * C * sizeof(T);
-
-  if (threadIdx.x == 0) {
-    mbar_init(bar, 1);
-    mbar_fence_init();
-  }
-
-  float q[HD];
-  float acc[HD];
-  int my_vox = 0, my_rel = 0, my_region = 0;
-  if (active) {
-    const int row = d.x + q_first + r;
-    my_vox = __ldg(p.pack_perm + row);
-    const int m = __ldg(p.pack_meta + row);
-    my_rel = meta_rel(m) + p.rel_off;
-    my_region = meta_region(m);
-    const unsigned char* src =
-        reinterpret_cast<const unsigned char*>(p.qkv) + ((int64_t)my_vox * 3 * C + h * HD) * sizeof(T);
-    constexpr int V = Elt<T>::kVec;
-#pragma unroll
-    for (int e = 0; e < HD; e += V) {
-      uint4 u = __ldg(reinterpret_cast<const uint4*>(src + e * sizeof(T)));
-      float f[V];
-      Elt<T>::unpack(u, f);
-#pragma unroll
-      for (int x = 0; x < V; ++x) q[e + x] = f[x] * p.scale;
-    }
-  }
-  const float* table_h = p.table + h;
-  __syncthreads();  // barrier initialised
-
-  const int n_tiles = (keys_total + tile - 1) / tile;
-  const int n_pass = p.attn_vals ? 2 : 1;
-  float m_run = 0.f, l_run = 0.f;  // upstream's row maximum starts from 0 (ops.cu:137)
-  float inv_l = 0.f;
-  uint32_t phase = 0;
-  int64_t coo_base = 0;
-  if (n_pass == 2 && active) {
-    const int kwin = __ldg(p.pack_win + d.w + wl);
-    coo_base = ((int64_t)__ldg(p.coo_start + kwin) * H + (int64_t)h * c * c) +
-               (int64_t)(big ? q_first + r : r - wl * c) * c;
-  }
-#pragma unroll
-  for (int e = 0; e < HD; ++e) acc[e] = 0.f;
-
-  for (int pass = 0; pass < n_pass; ++pass) {
-    for (int t = 0; t < n_tiles; ++t) {
-      const int k0 = t * tile;
-      const int rows_t = min(tile, keys_total - k0);
-      if (pass == 0 || n_tiles > 1) {
-        if (threadIdx.x == 0) mbar_expect_tx(bar, rows_t * row_bytes);
-        if ((int)threadIdx.x < rows_t) {
-          const int row = d.x + k0 + threadIdx.x;
-          const int vj = __ldg(p.pack_perm + row);
-          kmeta[threadIdx.x] = __ldg(p.pack_meta + row);
-          bulk_g2s(rows + (size_t)threadIdx.x * p.row_stride,
-                   reinterpret_cast<const unsigned char*>(p.qkv) + ((int64_t)vj * 3 * C + C) * sizeof(T), row_bytes,
-                   bar);
-        }
-        __syncthreads();  // kmeta visible
-        if (!mbar_wait_bounded(bar, phase)) {
-          atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
-          return;
-        }
-        phase ^= 1;
-      }
-      if (active) {
-        const int jb = max(kbeg, k0), je = min(kend, k0 + rows_t);
-        for (int j = jb; j < je; j += kKeyChunk) {
-          float s[kKeyChunk];
-#pragma unroll
-          for (int u = 0; u < kKeyChunk; ++u) {
-            const int jj = min(j + u, je - 1) - k0;
-            const unsigned char* krow = rows + (size_t)jj * p.row_stride + h * HD * sizeof(T);
-            float sc = dot_row<T, HD>(q, krow);
-            const int km = kmeta[jj];
-            sc += __ldg(table_h + (my_rel - meta_rel(km)) * H);
-            if (p.use_mask && my_region != meta_region(km)) sc += -100.0f;
-            s[u] = (j + u < je) ? sc : -INFINITY;
-          }
-          if (pass == 0) {
-            float mc = s[0];
-#pragma unroll
-            for (int u = 1; u < kKeyChunk; ++u) mc = fmaxf(mc, s[u]);
-            if (mc > m_run) {
-              const float corr = expf(m_run - mc);
-              l_run *= corr;
-#pragma unroll
-              for (int e = 0; e < HD; ++e) acc[e] *= corr;
-              m_run = mc;
-            }
-#pragma unroll
-            for (int u = 0; u < kKeyChunk; ++u) {
-              const float pu = expf(s[u] - m_run);
-              l_run += pu;
-              const int jj = min(j + u, je - 1) - k0;
-              const unsigned char* vrow = rows + (size_t)jj * p.row_stride + (C + h * HD) * sizeof(T);
-              constexpr int V = Elt<T>::kVec;
-#pragma unroll
-              for (int e = 0; e < HD; e += V) {
-                uint4 uv = *reinterpret_cast<const uint4*>(vrow + e * sizeof(T));
-                float f[V];
-                Elt<T>::unpack(uv, f);
-#pragma unroll
-                for (int x = 0; x < V; ++x) acc[e + x] = fmaf(pu, f[x], acc[e + x]);
-              }
-            }
-          } else {
-            T* dst = reinterpret_cast<T*>(p.attn_vals) + coo_base + (j - kbeg);
-#pragma unroll
-            for (int u = 0; u < kKeyChunk; ++u) {
-              if (j + u < je) {
-                float f = expf(s[u] - m_run) * inv_l;
-                if constexpr (sizeof(T) == 4) {
-                  reinterpret_cast<float*>(dst)[u] = f;
-                } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-                  dst[u] = __float2bfloat16_rn(f);
-                } else {
-                  dst[u] = __float2half_rn(f);
-                }
-              }
-            }
-          }
-        }
-      }
-      if (n_tiles > 1) __syncthreads();  // everyone done with this tile before it is overwritten
-    }
-    if (pass == 0) inv_l = 1.0f / (l_run + 1e-8f);
-  }
-
-  if (active) {
-    const float denom = l_run + 1e-8f;  // ops.cu:164
-    unsigned char* dst = reinterpret_cast<unsigned char*>(p.out) + ((int64_t)my_vox * C + h * HD) * sizeof(T);
-    constexpr int V = Elt<T>::kVec;
-#pragma unroll
-    for (int e = 0; e < HD; e += V) {
-      float f[V];
-#pragma unroll
-      for (int x = 0; x < V; ++x) f[x] = acc[e + x] / denom;
-      *reinterpret_cast<uint4*>(dst + e * sizeof(T)) = Elt<T>::pack(f);
-    }
-  }
-}
-
-template <typename T, int HD>
-static int launch_attn(const AttnParams& p, int grid, int threads, size_t smem, cudaStream_t stream) {
-  // Two register budgets: up to 256 threads per item (>=3 items per SM) or up to 1024.
-  if (threads <= 256) {
-    auto kern = k_attn_fused<T, HD, 256, 2>;
+template <typename T, int HD, bool kTableSmem>
+static int launch_attn(const AttnParams& p, int threads, size_t smem, cudaStream_t stream) {
+  int dev = 0, sms = 0;
+  SSW_CUDA_TRY(cudaGetDevice(&dev));
+  SSW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if (threads <= 384) {
+    auto kern = k_attn_fused<T, HD, kTableSmem, 384>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, threads, smem, stream>>>(p);
+    kern<<<sms, threads, smem, stream>>>(p);
+  } else if (threads <= 512) {
+    auto kern = k_attn_fused<T, HD, kTableSmem, 512>;
+    SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<sms, threads, smem, stream>>>(p);
   } else {
-    auto kern = k_attn_fused<T, HD, 1024, 1>;
+    auto kern = k_attn_fused<T, HD, kTableSmem, 1024>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, threads, smem, stream>>>(p);
+    kern<<<sms, threads, smem, stream>>>(p);
   }
   SSW_LAUNCH_CHECK("k_attn_fused");
   return SSW_OK;
 }
 
 template <typename T>
-static int dispatch_hd(const AttnParams& p, int hd, int grid, int threads, size_t smem, cudaStream_t stream) {
-  switch (hd) {
-    case 16: return launch_attn<T, 16>(p, grid, threads, smem, stream);
-    case 32: return launch_attn<T, 32>(p, grid, threads, smem, stream);
-    default: return SSW_E_UNSUPPORTED;
-  }
+static int dispatch(const AttnParams& p, int hd, int threads, size_t smem, cudaStream_t stream) {
+  const bool ts = p.table_floats > 0;
+  if (hd == 16)
+    return ts ? launch_attn<T, 16, true>(p, threads, smem, stream) : launch_attn<T, 16, false>(p, threads, smem, stream);
+  if (hd == 32)
+    return ts ? launch_attn<T, 32, true>(p, threads, smem, stream) : launch_attn<T, 32, false>(p, threads, smem, stream);
+  return SSW_E_UNSUPPORTED;
 }
 
 }  // namespace ssw
 
 using namespace ssw;
+
+extern "C" int32_t ssw_default_tile_rows(int32_t heads, int32_t head_dim, int dtype, const int32_t rpb_window[3]) {
+  if (heads <= 0 || head_dim <= 0 || !rpb_window) return 0;
+  const int elt = dtype == SSW_F32 ? 4 : 2;
+  // the largest tile that still leaves three pipeline stages
+  static const int kTiles[] = {64, 48, 32, 24, 16};
+  for (int tile : kTiles)
+    if (kernel_shape(tile, heads, head_dim, elt, rpb_window).stages >= 3) return tile;
+  return 8;
+}
 
 extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t head_dim, const ssw_plan_layout* L,
                               const int32_t* plan, const float* table, const int32_t rpb_window[3], float scale,
@@ -312,8 +697,10 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return SSW_E_INVALID;
   if ((head_dim * elt) % 16) return SSW_E_UNSUPPORTED;
   const int tile = L->tile_rows;
-  const int threads = tile * heads;
-  if (threads > 1024) return SSW_E_INVALID;
+  if (tile > kMaxTile) return SSW_E_UNSUPPORTED;
+  const KernelShape s = kernel_shape(tile, heads, head_dim, elt, rpb_window);
+  if (s.stages < 2 || s.smem > 227 * 1024) return SSW_E_UNSUPPORTED;
+  const int threads = s.groups * s.group_threads + 32;
   AttnParams p;
   p.qkv = qkv;
   p.out = out;
@@ -330,16 +717,21 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   p.H = heads;
   p.C = C;
   p.tile = tile;
+  p.HG = s.hg;
+  p.group_threads = s.group_threads;
+  p.groups = s.groups;
+  p.stages = s.stages;
   p.scale = scale;
   p.use_mask = use_mask;
-  p.row_stride = 2 * C * elt + 16;  // +16 B skews rows across shared-memory banks
-  const size_t smem = 16 + ((tile * 4 + 15) & ~15) + (size_t)tile * p.row_stride;
-  if (smem > 227 * 1024) return SSW_E_UNSUPPORTED;
+  p.row_stride = s.row_stride;
+  p.stage_bytes = s.stage_bytes;
+  p.out_off = s.out_off;
+  p.table_floats = s.table_floats;
   cudaStream_t stream = (cudaStream_t)stream_;
   switch (dtype) {
-    case SSW_F32: return dispatch_hd<float>(p, head_dim, L->pack_cap, threads, smem, stream);
-    case SSW_BF16: return dispatch_hd<__nv_bfloat16>(p, head_dim, L->pack_cap, threads, smem, stream);
-    case SSW_F16: return dispatch_hd<__half>(p, head_dim, L->pack_cap, threads, smem, stream);
+    case SSW_F32: return dispatch<float>(p, head_dim, threads, s.smem, stream);
+    case SSW_BF16: return dispatch<__nv_bfloat16>(p, head_dim, threads, s.smem, stream);
+    case SSW_F16: return dispatch<__half>(p, head_dim, threads, s.smem, stream);
   }
   return SSW_E_INVALID;
 }

@@ -264,6 +264,7 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
       bins.rowstart[cc] = e2.rows;
       bins.packstart[cc] = (int)e2.sq;
       bins.fill[cc] = 0;
+      if (cc == tile + 1) header[SSW_H_PACKS_SMALL] = (int)e2.sq;
     }
     carry = tri_add(carry, tot2);
   }
@@ -271,6 +272,7 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
     win_start[W] = N;
     coo_start[W] = (int)sq;
     header[SSW_H_PACKS] = (int)carry.sq;
+    if (tile + 1 > n_per_window + 1) header[SSW_H_PACKS_SMALL] = (int)carry.sq;
     header[SSW_H_TILE] = tile;
     if (sq >= (1ull << 31)) atomicOr(reinterpret_cast<unsigned*>(header + SSW_H_ERROR), SSW_DEV_COO_RANGE);
   }
@@ -417,23 +419,13 @@ extern "C" int ssw_window_keys(const int32_t* coords, int64_t n_vox, const ssw_g
   return SSW_OK;
 }
 
-extern "C" int32_t ssw_default_tile_rows(int32_t heads, int32_t head_dim, int dtype) {
-  if (heads <= 0 || head_dim <= 0) return 0;
-  int elt = dtype == SSW_F32 ? 4 : 2;
-  int64_t row_bytes = 2ll * heads * head_dim * elt + 16;
-  int tile = 64;
-  // keep one work item within 1024 threads and ~100 KB of staged K/V rows
-  while (tile > 8 && (tile * heads > 1024 || tile * row_bytes > 100 * 1024)) tile >>= 1;
-  return tile;
-}
-
 extern "C" int ssw_plan_layout_init(ssw_plan_layout* L, int64_t n_vox, int32_t n_windows, int32_t n_per_window,
                                     int32_t tile_rows) {
   if (!L || n_vox < 0 || n_windows <= 0 || n_per_window <= 0) return SSW_E_INVALID;
   if (n_per_window > kMaxPerWindow) return SSW_E_UNSUPPORTED;
   if (n_vox >= (int64_t(1) << 31) - 4096) return SSW_E_RANGE;
   if (tile_rows <= 0) tile_rows = 64;
-  if (tile_rows > 1024) return SSW_E_INVALID;
+  if (tile_rows > 64) return SSW_E_INVALID;
   L->n_vox = n_vox;
   L->n_windows = n_windows;
   L->n_per_window = n_per_window;

@@ -14,7 +14,7 @@ BF16_TOL = 2e-2   # same form, bf16 inputs/outputs against the fp32 oracle
 def _plan(case, dev, dtype, from_coords=True, tile=None):
     from sparseswin3d_b200 import attention, window
 
-    tile = tile or attention.default_tile_rows(case["heads"], case["head_dim"], dtype)
+    tile = tile or attention.default_tile_rows(case["heads"], case["head_dim"], dtype, case["window"])
     if from_coords:
         g = window.resolve_geometry(case["batch"], case["dims"], case["window"], case["shift"])
         return window.bucket_windows(coords=case["coords"].to(dev), geom=g, rpb_window=case["window"], tile_rows=tile)
