@@ -140,7 +140,7 @@ def run_ours(args):
     qkv = [q.to(dev) for q in qkv_h]
     outs = [torch.empty(N_VOX, C, dtype=dtype, device=dev) for _ in range(n_sets)]
     geoms = [window.resolve_geometry(1, dims, WINDOW, (0, 0, 0)), window.resolve_geometry(1, dims, WINDOW, SHIFT)]
-    tile = attention.default_tile_rows(HEADS, HEAD_DIM, dtype, WINDOW)
+    tile = args.tile or attention.default_tile_rows(HEADS, HEAD_DIM, dtype, WINDOW)
     scale = HEAD_DIM ** -0.5
     scratch = torch.empty(1, dtype=torch.int32, device=dev)
 
@@ -393,6 +393,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
+    ap.add_argument("--tile", type=int, default=0, help="override the rows per work item (experiments)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     args = ap.parse_args()

@@ -163,6 +163,84 @@ int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t head_dim,
                    const float* table, const int32_t rpb_window[3], float scale, int use_mask,
                    void* out, void* attn_vals, void* stream);
 
+/* ---- COO operator surface ----------------------------------------------------------
+ * The unfused operators upstream exports from sparse_swin/ops.cpp:7-18, with upstream's layouts.
+ * Functions whose output size depends on the data come in two steps: a *_plan call that leaves
+ * the counts in a small device array (the caller reads them back, as upstream does with .item())
+ * and a run call that fills caller-allocated outputs. */
+
+/* flatten_indices (ops.cpp:11, ops.cu:232-273).  indices [D, nnz] int32, sizes: D host ints; the
+ * hash is accumulated in int32 and wraps exactly like upstream's. */
+int ssw_flatten_indices(const int32_t* indices, int32_t D, int64_t nnz, const int32_t* sizes, int32_t* out,
+                        void* stream);
+
+/* sort_indices (ops.cpp:12, ops.cu:276-289): stable argsort of int32 keys, signed order. */
+int64_t ssw_argsort_workspace_bytes(int64_t n);
+int ssw_argsort_i32(const int32_t* keys, int64_t n, int32_t* perm_out, void* workspace, int64_t workspace_bytes,
+                    void* stream);
+
+/* return_inverse (ops.cpp:13, ops.cu:718-730): rank of every x[i] among the distinct values present
+ * (all in [0, maxnum)); count_out[0] (device) = number of distinct values; err (device int32) gets
+ * SSW_DEV_BAD_COORD or-ed in when a value lies outside [0, maxnum). */
+int64_t ssw_return_inverse_workspace_bytes(int64_t maxnum);
+int ssw_return_inverse(const int32_t* x, int64_t n, int64_t maxnum, int32_t* rank_out, int32_t* count_out,
+                       int32_t* err, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* unique_consecutive_indices (ops.cpp:14, ops.cu:32-103): inverse of unique_consecutive. */
+int64_t ssw_scan_workspace_bytes(int64_t n);
+int ssw_unique_consecutive_inverse(const int32_t* x, int64_t n, int32_t* out, void* workspace, int64_t workspace_bytes,
+                                   void* stream);
+
+/* qkv_sparse_indices (ops.cpp:10, ops.cu:293-335).  indices [N,2] int32; `plan` is the result of
+ * ssw_bucket_windows on the same indices.  idx_qv / idx_k [4, N*heads*c] are the UNSORTED index
+ * blocks in (voxel, head, channel) order with rows (window, head, pos, ch) / (window, head, ch,
+ * pos); perm_qv / perm_k are the argsorts of their row-major keys, produced from the bucketing
+ * instead of two radix sorts over N*heads*c keys (so they stay lexicographic even where upstream's
+ * int32 hash would wrap). */
+int ssw_qkv_sparse_indices(const int32_t* indices, int64_t n_vox, int32_t heads, int32_t c, const ssw_plan_layout* L,
+                           const int32_t* plan, int32_t* idx_qv, int32_t* perm_qv, int32_t* idx_k, int32_t* perm_k,
+                           void* stream);
+
+/* matmul_cuda_naive (ops.cpp:8, ops.cu:1034-1088 -> 788-943), in two steps.
+ * ssw_coo_block_plan reads the index rows of the operand that defines the blocks (the LHS for
+ * "q_k", the RHS for "qk_v"; rows of `row_len` = head_dim elements) and writes
+ *   blk_start [rows+1]: first row of every (window, head) block, then the row count
+ *   sq_start  [rows+1]: exclusive sums of c_b^2
+ *   counts (device int64[2]): number of blocks, sum of c_b^2.
+ * ssw_coo_matmul (mul_type 0 = "q_k", 1 = "qk_v") then fills out_v [total], out_idx [4,total] and
+ * c_out [n_blocks] (upstream's `_c`), total = sum c^2 for q_k and the RHS nnz for qk_v.  The
+ * products are sequential FMA chains in upstream's order (ops.cu:371-375, 411-415). */
+int64_t ssw_coo_plan_workspace_bytes(int64_t n_rows);
+int ssw_coo_block_plan(const int32_t* idx, int64_t nnz, int32_t row_len, int32_t* blk_start, int32_t* sq_start,
+                       int64_t* counts, void* workspace, int64_t workspace_bytes, void* stream);
+int ssw_coo_matmul(int mul_type, int dtype, const void* m1_v, const int32_t* m1_idx, int64_t nnz1, const void* m2_v,
+                   int32_t C, const int32_t* blk_start, const int32_t* sq_start, int64_t n_blocks, int64_t total,
+                   void* out_v, int32_t* out_idx, int32_t* c_out, const int64_t* counts, void* stream);
+
+/* Offsets for the `_c`-keyed backward operators: exclusive sums of c and of c^2, [nb+1] each. */
+int ssw_coo_offsets_from_counts(const int32_t* c, int64_t nb, int32_t* cstart, int32_t* sqstart, void* workspace,
+                                int64_t workspace_bytes, void* stream);
+/* matmul_grad_cuda_naive (ops.cpp:9, ops.cu:945-1031): mode 0 "rc_cr", 1 "rr_rc", 2 "cr_rr". */
+int ssw_coo_matmul_grad(int mode, int dtype, const void* m1_v, const void* m2_v, const int32_t* cstart,
+                        const int32_t* sqstart, int64_t nb, int32_t C, void* out_v, void* stream);
+/* qkv_transpose (ops.cpp:17, ops.cu:663-715): rr = 0 "rc", rr = 1 "rr". */
+int ssw_coo_block_transpose(int rr, int dtype, const void* m1_v, const int32_t* cstart, const int32_t* sqstart,
+                            int64_t nb, int32_t C, void* out_v, void* stream);
+
+/* softmax_last_dim_forward / _backward (ops.cpp:15-16, ops.cu:128-194), fp32.  row_ids: sorted,
+ * consecutive from 0; n_rows = row_ids[nnz-1] + 1 (host value, as upstream's .item()); row_start:
+ * caller scratch [n_rows + 1].  Forward keeps upstream's max(0, .) and +1e-8. */
+int ssw_softmax_rows_fwd(const int32_t* row_ids, int64_t nnz, int32_t n_rows, const float* vals, float* out,
+                         int32_t* row_start, void* stream);
+int ssw_softmax_rows_bwd(const int32_t* row_ids, int64_t nnz, int32_t n_rows, const float* y, const float* g,
+                         float* out, int32_t* row_start, void* stream);
+
+/* sp_add_rpb + sp_add_mask (swin3d_base.py:557-581) in one pass: vals + dense[h, pos_i, pos_j]
+ * (dense [H, n, n] of the value dtype, may be NULL) and -100 where mask[w % mask_windows, pos_i] !=
+ * mask[..., pos_j] (mask [mask_windows, mask_n] int8, may be NULL). */
+int ssw_coo_add_bias_mask(int dtype, const void* vals, const int32_t* idx, int64_t nnz, const void* dense, int32_t n,
+                          const int8_t* mask, int32_t mask_windows, int32_t mask_n, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

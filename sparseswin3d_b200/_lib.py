@@ -57,6 +57,23 @@ def _load() -> C.CDLL:
         "ssw_plan_layout_init": (C.c_int, [P(PlanLayout), i64, i32, i32, i32]),
         "ssw_bucket_windows": (C.c_int, [vp, P(Geometry), vp, vp, i32, P(i32), P(PlanLayout), vp, vp, vp]),
         "ssw_attn_fused": (C.c_int, [vp, C.c_int, i32, i32, P(PlanLayout), vp, vp, P(i32), f32, C.c_int, vp, vp, vp]),
+        "ssw_flatten_indices": (C.c_int, [vp, i32, i64, P(i32), vp, vp]),
+        "ssw_argsort_workspace_bytes": (i64, [i64]),
+        "ssw_argsort_i32": (C.c_int, [vp, i64, vp, vp, i64, vp]),
+        "ssw_return_inverse_workspace_bytes": (i64, [i64]),
+        "ssw_return_inverse": (C.c_int, [vp, i64, i64, vp, vp, vp, vp, i64, vp]),
+        "ssw_scan_workspace_bytes": (i64, [i64]),
+        "ssw_unique_consecutive_inverse": (C.c_int, [vp, i64, vp, vp, i64, vp]),
+        "ssw_qkv_sparse_indices": (C.c_int, [vp, i64, i32, i32, P(PlanLayout), vp, vp, vp, vp, vp, vp]),
+        "ssw_coo_plan_workspace_bytes": (i64, [i64]),
+        "ssw_coo_block_plan": (C.c_int, [vp, i64, i32, vp, vp, vp, vp, i64, vp]),
+        "ssw_coo_matmul": (C.c_int, [C.c_int, C.c_int, vp, vp, i64, vp, i32, vp, vp, i64, i64, vp, vp, vp, vp, vp]),
+        "ssw_coo_offsets_from_counts": (C.c_int, [vp, i64, vp, vp, vp, i64, vp]),
+        "ssw_coo_matmul_grad": (C.c_int, [C.c_int, C.c_int, vp, vp, vp, vp, i64, i32, vp, vp]),
+        "ssw_coo_block_transpose": (C.c_int, [C.c_int, C.c_int, vp, vp, vp, i64, i32, vp, vp]),
+        "ssw_softmax_rows_fwd": (C.c_int, [vp, i64, i32, vp, vp, vp, vp]),
+        "ssw_softmax_rows_bwd": (C.c_int, [vp, i64, i32, vp, vp, vp, vp, vp]),
+        "ssw_coo_add_bias_mask": (C.c_int, [C.c_int, vp, vp, i64, vp, i32, vp, i32, i32, vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)  # AttributeError here = header and library disagree

@@ -110,8 +110,37 @@ class WindowAttentionSparse(nn.Module):
         core = window_attention_fused(qkv, plan, self.relative_position_bias_table, self.scale, use_mask)
         return self.proj_drop(self.proj(core))
 
-    @torch.no_grad()
-    def forward(self, x, mask, plan: Optional[WindowPlan] = None):
-        if plan is None:
-            plan = self.plan(x, mask, x.features.dtype)
-        return x.replace_feature(self.forward_features(x.features, plan, mask is not None))
+    def forward_unfused(self, x, mask):
+        """Upstream's forward, operator by operator (swin3d_base.py:654-677), on the COO operator
+        surface; differentiable through the same autograd Functions upstream defines."""
+        from . import ops
+        from .sparse_tensor import qkv_sparse_cuda, softmax_last_dim, sp_add_mask, sp_add_rpb, spspmm_block_naive
+
+        n = x.spatial_shape[0]
+        b = x.batch_size
+        c = x.features.shape[-1]
+        qkv = self.qkv(x.features).reshape(-1, 3, self.num_heads, c // self.num_heads)
+        q, k_t, v = qkv_sparse_cuda(qkv, x.indices, b, n)
+        q = q * self.scale
+        attn = spspmm_block_naive(q, k_t, "q_k")
+        bias = self.relative_position_bias_table[self.relative_position_index[:n, :n].reshape(-1)].reshape(n, n, -1)
+        bias = bias.permute(2, 0, 1).contiguous().to(attn.values.dtype)
+        attn = sp_add_rpb(attn, bias)
+        if mask is not None:
+            attn = sp_add_mask(attn, mask)
+        attn = softmax_last_dim(attn)
+        x_ = spspmm_block_naive(attn, v, "qk_v").permute((0, 2, 1, 3))
+        arg_sort = ops.return_inverse(ops.flatten_indices(x.indices.T.contiguous(), [b, n]), -1)[0]
+        x = x.replace_feature(x_.values.reshape(x.features.shape).index_select(0, arg_sort))
+        return x.replace_feature(self.proj_drop(self.proj(x.features)))
+
+    def forward(self, x, mask, plan: Optional[WindowPlan] = None, fused: Optional[bool] = None):
+        """fused=None picks the fused kernel unless autograd is recording (it has no backward)."""
+        if fused is None:
+            fused = not (torch.is_grad_enabled() and (x.features.requires_grad or self.qkv.weight.requires_grad))
+        if not fused:
+            return self.forward_unfused(x, mask)
+        with torch.no_grad():
+            if plan is None:
+                plan = self.plan(x, mask, x.features.dtype)
+            return x.replace_feature(self.forward_features(x.features, plan, mask is not None))

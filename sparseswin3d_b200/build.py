@@ -44,7 +44,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     nvcc = _nvcc()
     OBJ.mkdir(exist_ok=True)
     flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-             "-Xcompiler", "-fPIC", "-I", str(INCLUDE)]
+             "--extended-lambda", "-Xcompiler", "-fPIC", "-I", str(INCLUDE)]
     if verbose:
         flags += ["-Xptxas", "-v"]
 
