@@ -144,6 +144,24 @@ int ssw_bucket_windows(const int32_t* coords, const ssw_geometry* geom,
                        const int32_t rpb_window[3],
                        const ssw_plan_layout* L, int32_t* plan, int32_t* scratch, void* stream);
 
+/* No counterpart in upstream.  ssw_bucket_windows for callers that cannot hand over scratch memory:
+ * hosts that embed this library inside another framework's memory plan, or run under a runtime
+ * that forbids device allocation once it has started, have no buffer to pass as `scratch`.  The
+ * scratch is a fixed 16 MiB (4 Mi int32) array inside the library image instead, resident on every
+ * device that loads the library until the process exits.  Same arguments and results as
+ * ssw_bucket_windows minus `scratch`; the caller still provides `plan`.  Returns SSW_E_WORKSPACE
+ * (details in ssw_last_cuda_error) when L->scratch_ints exceeds
+ * ssw_bucket_windows_static_capacity().  The function allocates nothing, neither through CUDA nor
+ * through any library.  The first call on a device looks up the array's device address; make that
+ * first call outside any stream capture.  All calls on a device share the one array and each call
+ * clears the part it uses, so two calls whose kernels overlap on the GPU (different streams)
+ * corrupt each other: serialise them. */
+int64_t ssw_bucket_windows_static_capacity(void);
+int ssw_bucket_windows_static(const int32_t* coords, const ssw_geometry* geom,
+                              const int32_t* indices, const int8_t* mask, int32_t mask_windows,
+                              const int32_t rpb_window[3],
+                              const ssw_plan_layout* L, int32_t* plan, void* stream);
+
 /* ---- fused W-MSA / SW-MSA core ----------------------------------------------------
  * Replaces, in one kernel per call, everything WindowAttentionSparse.forward does
  * between its two Linear layers (swin3d_base.py:659-675): qkv_sparse_cuda (:483-498),

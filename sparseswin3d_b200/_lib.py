@@ -56,6 +56,8 @@ def _load() -> C.CDLL:
         "ssw_default_tile_rows": (i32, [i32, i32, C.c_int, P(i32)]),
         "ssw_plan_layout_init": (C.c_int, [P(PlanLayout), i64, i32, i32, i32]),
         "ssw_bucket_windows": (C.c_int, [vp, P(Geometry), vp, vp, i32, P(i32), P(PlanLayout), vp, vp, vp]),
+        "ssw_bucket_windows_static_capacity": (i64, []),
+        "ssw_bucket_windows_static": (C.c_int, [vp, P(Geometry), vp, vp, i32, P(i32), P(PlanLayout), vp, vp]),
         "ssw_attn_fused": (C.c_int, [vp, C.c_int, i32, i32, P(PlanLayout), vp, vp, P(i32), f32, C.c_int, vp, vp, vp]),
         "ssw_flatten_indices": (C.c_int, [vp, i32, i64, P(i32), vp, vp]),
         "ssw_argsort_workspace_bytes": (i64, [i64]),
@@ -92,7 +94,7 @@ class SswError(RuntimeError):
 def check(status: int, what: str) -> None:
     if status != SSW_OK:
         msg = lib.ssw_status_string(status).decode()
-        if status == -4:
+        if status in (-4, -5):
             msg += ": " + lib.ssw_last_cuda_error().decode()
         raise SswError(f"{what}: {msg} (status {status})")
 

@@ -12,6 +12,8 @@
 //   k_order    : window -> slot inside its occupancy bin; work-item descriptors
 //   k_scatter  : per voxel, rank inside its window = popcount of lower bitmap bits -> perm,
 //                inverse perm, pack-order perm and per-row metadata
+#include <stdio.h>
+
 #include "ssw_common.cuh"
 
 namespace ssw {
@@ -511,4 +513,45 @@ extern "C" int ssw_bucket_windows(const int32_t* coords, const ssw_geometry* geo
                                             plan + L->off_pack_perm, plan + L->off_pack_meta);
   SSW_LAUNCH_CHECK("k_scatter");
   return SSW_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Bucketing without a caller-provided scratch buffer
+// ---------------------------------------------------------------------------------------------
+// Some hosts of this library cannot give it scratch memory: a plugin that runs inside another
+// framework's memory plan, or under a runtime that forbids device allocation after start-up, has
+// nowhere to get the per-window counters and occupancy bitmaps from (cudaMalloc is off limits and
+// no allocator handle crosses the C ABI).  For them the scratch lives here, in a fixed array that
+// is part of the loaded module: 4 Mi int32 = 16 MiB, held by every device that loads the library
+// until the process exits.
+constexpr int64_t kStaticScratchInts = int64_t(4) << 20;
+static __device__ __align__(256) int32_t g_static_scratch[kStaticScratchInts];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the
+// address a kernel can use has to be asked for, once per device, with that device current.
+static int32_t* g_static_scratch_ptr[64] = {nullptr};
+
+extern "C" int64_t ssw_bucket_windows_static_capacity(void) { return kStaticScratchInts; }
+
+extern "C" int ssw_bucket_windows_static(const int32_t* coords, const ssw_geometry* geom, const int32_t* indices,
+                                         const int8_t* mask, int32_t mask_windows, const int32_t rpb_window[3],
+                                         const ssw_plan_layout* L, int32_t* plan, void* stream) {
+  if (!L) return SSW_E_INVALID;
+  if (L->scratch_ints > kStaticScratchInts) {
+    char msg[160];
+    snprintf(msg, sizeof(msg), "ssw_bucket_windows_static: needs %lld scratch ints, the built-in array holds %lld",
+             (long long)L->scratch_ints, (long long)kStaticScratchInts);
+    ssw::set_error_text(msg);
+    return SSW_E_WORKSPACE;
+  }
+  int dev = 0;
+  SSW_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return SSW_E_UNSUPPORTED;
+  if (!g_static_scratch_ptr[dev]) {  // set-up: first call on this device
+    void* p = nullptr;
+    SSW_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    g_static_scratch_ptr[dev] = static_cast<int32_t*>(p);
+  }
+  return ssw_bucket_windows(coords, geom, indices, mask, mask_windows, rpb_window, L, plan, g_static_scratch_ptr[dev],
+                            stream);
 }

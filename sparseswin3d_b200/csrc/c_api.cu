@@ -9,6 +9,7 @@ static thread_local char g_cuda_error[256] = "";
 void set_cuda_error(cudaError_t e, const char* where) {
   snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
 }
+void set_error_text(const char* text) { snprintf(g_cuda_error, sizeof(g_cuda_error), "%s", text); }
 }  // namespace ssw
 
 extern "C" const char* ssw_status_string(int status) {

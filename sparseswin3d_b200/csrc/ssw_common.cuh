@@ -12,6 +12,7 @@ namespace ssw {
 
 // ---- host-side error plumbing ---------------------------------------------------------
 void set_cuda_error(cudaError_t e, const char* where);
+void set_error_text(const char* text);  // shown by ssw_last_cuda_error() next to a non-CUDA status
 
 #define SSW_CUDA_TRY(expr)                                   \
   do {                                                       \
