@@ -58,14 +58,16 @@ struct AttnParams {
 };
 
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kKeyChunk = 4;
 
 // Shared memory: [barriers 256 B][bias table][stage 0][stage 1]...
-// Stage: [desc int4][vox int[kMaxTile]][kmeta int2[kMaxTile]][rows tile*row_stride][16-bit out staging]
+// Stage: [desc int4][vox int[kMaxTile]][rows tile*row_stride][16-bit out staging]
+// Row:   [q | k | v as 3*C floats][meta int2 {byte offset of the key's bias-table row,
+//         region | (query-side relative-position code << 8)}][8 B unused]
+// The 16 bytes after the data skew consecutive rows across the shared-memory banks and carry the
+// per-row metadata, so one base pointer reaches both a key's channels and its metadata.
 constexpr int kBarBytes = 256;
 constexpr int kStageVoxOff = 16;
-constexpr int kStageMetaOff = kStageVoxOff + kMaxTile * 4;
-constexpr int kStageRowsOff = kStageMetaOff + kMaxTile * 8;
+constexpr int kStageRowsOff = kStageVoxOff + kMaxTile * 4;
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -224,68 +226,107 @@ __device__ __forceinline__ bool widen_rows(unsigned char* rows, int row_stride, 
   return ok;
 }
 
-// Keys [jb, je) of my window, staged at `rows` (row index = key - k0).  `k_off` is the byte offset
-// of this head's k slice inside a row; v sits C floats further.  kEmit: second pass that writes
-// the normalised probabilities instead of accumulating.
-template <typename T, int HD, bool kEmit, bool kTableSmem>
-__device__ __forceinline__ void attend_keys(RowState<HD>& st, const unsigned char* rows, const int2* kmeta,
-                                            int row_stride, int k0, int jb, int je, int k_off, int C,
-                                            const float* table_h, bool use_mask, int my_region, float inv_l,
-                                            T* emit_dst) {
+// N keys starting at `kp` (= first key's row + byte offset of this head's k slice).  Scores are in
+// the log2 domain: q carries scale*log2(e), the shared-memory bias table is pre-multiplied.
+template <typename T, int HD, int N, bool kEmit, bool kTableSmem, bool kMask>
+__device__ __forceinline__ void attend_chunk(RowState<HD>& st, const unsigned char* kp, int row_stride, int meta_off,
+                                             int v_off, const unsigned char* table_h, int my_region, float inv_l,
+                                             T* emit_dst) {
   const float mask_add = -100.0f * kLog2e;
-  for (int j = jb; j < je; j += kKeyChunk) {
-    float s[kKeyChunk];
-    const unsigned char* rowp[kKeyChunk];
+  float s[N];
 #pragma unroll
-    for (int u = 0; u < kKeyChunk; ++u) {
-      const int jj = min(j + u, je - 1) - k0;
-      rowp[u] = rows + (size_t)jj * row_stride + k_off;
-      const float4* kr = reinterpret_cast<const float4*>(rowp[u]);
-      // two independent partial sums per key keep the FMA dependency chains short
-      float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
+  for (int u = 0; u < N; ++u) {
+    const unsigned char* rp = kp + u * row_stride;
+    const float4* kr = reinterpret_cast<const float4*>(rp);
+    // two independent partial sums per key keep the FMA dependency chains short
+    float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int e = 0; e < HD / 4; ++e) {
+      const float4 kv = kr[e];
+      sa = __ffma2_rn(st.q[2 * e], make_float2(kv.x, kv.y), sa);
+      sb = __ffma2_rn(st.q[2 * e + 1], make_float2(kv.z, kv.w), sb);
+    }
+    const int2 km = *reinterpret_cast<const int2*>(rp + meta_off);
+    const float bias = kTableSmem ? *reinterpret_cast<const float*>(table_h - km.x)
+                                  : __ldg(reinterpret_cast<const float*>(table_h - km.x)) * kLog2e;
+    float sc = ((sa.x + sb.x) + (sa.y + sb.y)) + bias;
+    if (kMask && my_region != (km.y & 31)) sc += mask_add;
+    s[u] = sc;
+  }
+  if constexpr (!kEmit) {
+    float mc = s[0];
+#pragma unroll
+    for (int u = 1; u < N; ++u) mc = fmaxf(mc, s[u]);
+    if (mc > st.m) {
+      const float corr = fast_exp2(st.m - mc);
+      st.l *= corr;
+      const float2 c2 = make_float2(corr, corr);
+#pragma unroll
+      for (int e = 0; e < HD / 2; ++e) st.acc[e] = __fmul2_rn(st.acc[e], c2);
+      st.m = mc;
+    }
+#pragma unroll
+    for (int u = 0; u < N; ++u) {
+      const float pu = fast_exp2(s[u] - st.m);
+      st.l += pu;
+      const float2 p2 = make_float2(pu, pu);
+      const float4* vr = reinterpret_cast<const float4*>(kp + u * row_stride + v_off);
 #pragma unroll
       for (int e = 0; e < HD / 4; ++e) {
-        const float4 kv = kr[e];
-        sa = __ffma2_rn(st.q[2 * e], make_float2(kv.x, kv.y), sa);
-        sb = __ffma2_rn(st.q[2 * e + 1], make_float2(kv.z, kv.w), sb);
+        const float4 vv = vr[e];
+        st.acc[2 * e] = __ffma2_rn(p2, make_float2(vv.x, vv.y), st.acc[2 * e]);
+        st.acc[2 * e + 1] = __ffma2_rn(p2, make_float2(vv.z, vv.w), st.acc[2 * e + 1]);
       }
-      const int2 km = kmeta[jj];
-      const float bias = kTableSmem ? *(table_h - km.x) : __ldg(table_h - km.x);
-      float sc = (((sa.x + sb.x) + (sa.y + sb.y)) + bias) * kLog2e;
-      if (use_mask && my_region != (km.y & 31)) sc += mask_add;
-      s[u] = (j + u < je) ? sc : -INFINITY;
     }
-    if constexpr (!kEmit) {
-      float mc = s[0];
+  } else {
 #pragma unroll
-      for (int u = 1; u < kKeyChunk; ++u) mc = fmaxf(mc, s[u]);
-      if (mc > st.m) {
-        const float corr = fast_exp2(st.m - mc);
-        st.l *= corr;
-        const float2 c2 = make_float2(corr, corr);
-#pragma unroll
-        for (int e = 0; e < HD / 2; ++e) st.acc[e] = __fmul2_rn(st.acc[e], c2);
-        st.m = mc;
-      }
-#pragma unroll
-      for (int u = 0; u < kKeyChunk; ++u) {
-        const float pu = fast_exp2(s[u] - st.m);
-        st.l += pu;
-        const float2 p2 = make_float2(pu, pu);
-        const float4* vr = reinterpret_cast<const float4*>(rowp[u] + C * 4);
-#pragma unroll
-        for (int e = 0; e < HD / 4; ++e) {
-          const float4 vv = vr[e];
-          st.acc[2 * e] = __ffma2_rn(p2, make_float2(vv.x, vv.y), st.acc[2 * e]);
-          st.acc[2 * e + 1] = __ffma2_rn(p2, make_float2(vv.z, vv.w), st.acc[2 * e + 1]);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int u = 0; u < kKeyChunk; ++u)
-        if (j + u < je) emit_dst[j - jb + u] = from_float<T>(fast_exp2(s[u] - st.m) * inv_l);
-    }
+    for (int u = 0; u < N; ++u) emit_dst[u] = from_float<T>(fast_exp2(s[u] - st.m) * inv_l);
   }
+}
+
+// `n_keys` consecutive staged rows starting at row `first_row` of `rows`: full chunks of four keys,
+// then one chunk of the remaining 1-3 (every thread of an item has the same key count, so the
+// tail costs no divergence).  `k_off`: byte offset of this head's k slice inside a row; v sits C
+// floats further; the row's metadata sits at byte `data_bytes`.  kEmit: second pass that writes
+// the normalised probabilities instead of accumulating.
+template <typename T, int HD, bool kEmit, bool kTableSmem, bool kMask>
+__device__ __forceinline__ void attend_keys(RowState<HD>& st, const unsigned char* rows, int row_stride,
+                                            int data_bytes, int first_row, int n_keys, int k_off, int C,
+                                            const float* table_h, int my_region, float inv_l, T* emit_dst) {
+  const unsigned char* kp = rows + (size_t)first_row * row_stride + k_off;
+  const int meta_off = data_bytes - k_off;
+  const int v_off = C * 4;
+  const unsigned char* tab = reinterpret_cast<const unsigned char*>(table_h);
+  int j = 0;
+  for (; j + 4 <= n_keys; j += 4, kp += 4 * row_stride)
+    attend_chunk<T, HD, 4, kEmit, kTableSmem, kMask>(st, kp, row_stride, meta_off, v_off, tab, my_region, inv_l,
+                                                     emit_dst + j);
+  switch (n_keys - j) {
+    case 1:
+      attend_chunk<T, HD, 1, kEmit, kTableSmem, kMask>(st, kp, row_stride, meta_off, v_off, tab, my_region, inv_l,
+                                                       emit_dst + j);
+      break;
+    case 2:
+      attend_chunk<T, HD, 2, kEmit, kTableSmem, kMask>(st, kp, row_stride, meta_off, v_off, tab, my_region, inv_l,
+                                                       emit_dst + j);
+      break;
+    case 3:
+      attend_chunk<T, HD, 3, kEmit, kTableSmem, kMask>(st, kp, row_stride, meta_off, v_off, tab, my_region, inv_l,
+                                                       emit_dst + j);
+      break;
+    default: break;
+  }
+}
+template <typename T, int HD, bool kEmit, bool kTableSmem>
+__device__ __forceinline__ void attend_keys_m(bool use_mask, RowState<HD>& st, const unsigned char* rows,
+                                              int row_stride, int data_bytes, int first_row, int n_keys, int k_off,
+                                              int C, const float* table_h, int my_region, float inv_l, T* emit_dst) {
+  if (use_mask)
+    attend_keys<T, HD, kEmit, kTableSmem, true>(st, rows, row_stride, data_bytes, first_row, n_keys, k_off, C,
+                                                table_h, my_region, inv_l, emit_dst);
+  else
+    attend_keys<T, HD, kEmit, kTableSmem, false>(st, rows, row_stride, data_bytes, first_row, n_keys, k_off, C,
+                                                 table_h, my_region, inv_l, emit_dst);
 }
 
 // acc * inv_l as T, 16-byte vector stores (global or shared destination)
@@ -338,6 +379,8 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   const int copy_off = kHalf ? row_elems * 2 : 0;  // 16-bit rows land in the upper half of the fp32 row
   const uint32_t out_bytes = C * sizeof(T);
   const int n_hiter = H / p.HG;
+  const int data_bytes = row_elems * 4;      // fp32 payload of a staged row; its metadata follows
+  const float qscale = p.scale * kLog2e;     // scores are kept in the log2 domain
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -350,7 +393,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     mbar_fence_init();
   }
   if constexpr (kTableSmem)
-    for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) table_s[i] = __ldg(p.table + i);
+    for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) table_s[i] = __ldg(p.table + i) * kLog2e;
   __syncthreads();
 
   // ------------------------------------------------------------------------------------------
@@ -405,8 +448,8 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
         const int rr = lane + 32 * k;
         if (rr < nr) {
           reinterpret_cast<int*>(st + kStageVoxOff)[rr] = vox[k];
-          reinterpret_cast<int2*>(st + kStageMetaOff)[rr] =
-              make_int2(meta_rel(km[k]) * H, meta_region(km[k]) | ((meta_rel(km[k]) + p.rel_off) << 8));
+          *reinterpret_cast<int2*>(st + kStageRowsOff + (size_t)rr * p.row_stride + data_bytes) =
+              make_int2(meta_rel(km[k]) * H * 4, meta_region(km[k]) | ((meta_rel(km[k]) + p.rel_off) << 8));
         }
       }
       __syncwarp();
@@ -441,7 +484,6 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       const int use = i / S;
       unsigned char* sp = stage0 + (size_t)s * p.stage_bytes;
       unsigned char* rows = sp + kStageRowsOff;
-      const int2* kmeta = reinterpret_cast<const int2*>(sp + kStageMetaOff);
       if (!mbar_wait_bounded(full + s, use & 1)) {
         timed_out = true;
         break;
@@ -458,26 +500,26 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       }
       const bool row_active = thread_used && r < q_rows;
       const int wl = r / c;
-      const int kbeg = wl * c, kend = kbeg + c;
+      const int kbeg = wl * c;
       if (row_active) {
-        const int2 me = kmeta[r];
+        unsigned char* myrow = rows + (size_t)r * p.row_stride;
+        const int2 me = *reinterpret_cast<const int2*>(myrow + data_bytes);
         const int my_rel = (me.y >> 8) * H;
         const int my_region = me.y & 31;
-        unsigned char* myrow = rows + (size_t)r * p.row_stride;
         for (int hi = 0; hi < n_hiter; ++hi) {
           const int h = hi * p.HG + hg;
-          load_q_smem<HD>(reinterpret_cast<const float4*>(myrow) + (h * HD) / 4, p.scale, st.q);
+          load_q_smem<HD>(reinterpret_cast<const float4*>(myrow) + (h * HD) / 4, qscale, st.q);
           st.reset();
           const float* table_h = table_base + my_rel + h;
-          attend_keys<T, HD, false, kTableSmem>(st, rows, kmeta, p.row_stride, 0, kbeg, kend, (C + h * HD) * 4, C,
-                                                table_h, p.use_mask != 0, my_region, 0.f, nullptr);
+          attend_keys_m<T, HD, false, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, kbeg, c,
+                                                  (C + h * HD) * 4, C, table_h, my_region, 0.f, (T*)nullptr);
           const float inv_l = 1.0f / (st.l + 1e-8f);  // ops.cu:164
           if (p.attn_vals) {
             const int kwin = __ldg(p.pack_win + d.w + wl);
             T* dst = reinterpret_cast<T*>(p.attn_vals) + ((int64_t)__ldg(p.coo_start + kwin) * H + (int64_t)h * c * c) +
                      (int64_t)(r - kbeg) * c;
-            attend_keys<T, HD, true, kTableSmem>(st, rows, kmeta, p.row_stride, 0, kbeg, kend, (C + h * HD) * 4, C,
-                                                 table_h, p.use_mask != 0, my_region, inv_l, dst);
+            attend_keys_m<T, HD, true, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, kbeg, c,
+                                                   (C + h * HD) * 4, C, table_h, my_region, inv_l, dst);
           }
           // fp32: the slice that held my q; 16-bit: the stage's output area
           T* so = kHalf ? reinterpret_cast<T*>(sp + p.out_off + (size_t)r * out_bytes) + h * HD
@@ -518,7 +560,6 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   // Phase B: windows with c > tile; one query tile per item, key tiles through stage 0
   // ------------------------------------------------------------------------------------------
   unsigned char* rows = stage0 + kStageRowsOff;
-  int2* kmeta = reinterpret_cast<int2*>(stage0 + kStageMetaOff);
   uint32_t phase = 0;
   const int hg = threadIdx.x / tile;
   const int r = threadIdx.x - hg * tile;
@@ -545,7 +586,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       st.reset();
       float inv_l = 0.f;
       if (row_active)
-        load_q_global<T, HD>(reinterpret_cast<const T*>(p.qkv) + (int64_t)my_vox * 3 * C + h * HD, p.scale, st.q);
+        load_q_global<T, HD>(reinterpret_cast<const T*>(p.qkv) + (int64_t)my_vox * 3 * C + h * HD, qscale, st.q);
       const float* table_h = table_base + my_rel + h;
       T* emit = nullptr;
       if (n_pass == 2 && row_active) {
@@ -562,11 +603,12 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
             const int row = d.x + k0 + threadIdx.x;
             const int vj = __ldg(p.pack_perm + row);
             const int km = __ldg(p.pack_meta + row);
-            kmeta[threadIdx.x] = make_int2(meta_rel(km) * H, meta_region(km));
+            *reinterpret_cast<int2*>(rows + (size_t)threadIdx.x * p.row_stride + data_bytes) =
+                make_int2(meta_rel(km) * H * 4, meta_region(km));
             bulk_g2s(rows + (size_t)threadIdx.x * p.row_stride + copy_off,
                      reinterpret_cast<const T*>(p.qkv) + (int64_t)vj * 3 * C, copy_bytes, bbar);
           }
-          __syncthreads();  // kmeta visible
+          __syncthreads();  // row metadata visible
           const bool ok = mbar_wait_bounded(bbar, phase);
           if (__syncthreads_or(!ok)) {
             if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
@@ -580,13 +622,11 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
             });
           if (row_active) {
             if (pass == 0)
-              attend_keys<T, HD, false, kTableSmem>(st, rows, kmeta, p.row_stride, k0, k0, k0 + rows_t,
-                                                    (C + h * HD) * 4, C, table_h, p.use_mask != 0, my_region, 0.f,
-                                                    nullptr);
+              attend_keys_m<T, HD, false, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, 0, rows_t,
+                                                      (C + h * HD) * 4, C, table_h, my_region, 0.f, (T*)nullptr);
             else
-              attend_keys<T, HD, true, kTableSmem>(st, rows, kmeta, p.row_stride, k0, k0, k0 + rows_t,
-                                                   (C + h * HD) * 4, C, table_h, p.use_mask != 0, my_region, inv_l,
-                                                   emit + k0);
+              attend_keys_m<T, HD, true, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, 0, rows_t,
+                                                     (C + h * HD) * 4, C, table_h, my_region, inv_l, emit + k0);
           }
           __syncthreads();  // everyone done with this tile before it is overwritten
         }
