@@ -1,0 +1,84 @@
+// Device helpers shared by the fused attention kernels: fast exp2, mbarrier arrive, bulk (TMA)
+// stores, proxy fence, mbarrier-based group barrier, 16-bit widening and packing.
+#pragma once
+
+#include <type_traits>
+
+#include "ssw_common.cuh"
+
+namespace ssw {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// shared -> global bulk (TMA) store of `bytes` (multiple of 16, both addresses 16-byte aligned)
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// make generic-proxy writes to shared memory visible to the async proxy (bulk stores)
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Barrier among the warps of one consumer group, built on an mbarrier so that the wait is bounded.
+__device__ __forceinline__ bool group_barrier(uint64_t* bar, uint32_t& phase, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+  const bool ok = mbar_wait_bounded(bar, phase);
+  phase ^= 1;
+  return ok;
+}
+
+template <typename T>
+__device__ __forceinline__ void widen8(const uint4& u, float4& a, float4& b);
+template <>
+__device__ __forceinline__ void widen8<__nv_bfloat16>(const uint4& u, float4& a, float4& b) {
+  a = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                  __uint_as_float(u.y & 0xffff0000u));
+  b = make_float4(__uint_as_float(u.z << 16), __uint_as_float(u.z & 0xffff0000u), __uint_as_float(u.w << 16),
+                  __uint_as_float(u.w & 0xffff0000u));
+}
+template <>
+__device__ __forceinline__ void widen8<__half>(const uint4& u, float4& a, float4& b) {
+  float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+  float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+  float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&u.z));
+  float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&u.w));
+  a = make_float4(p0.x, p0.y, p1.x, p1.y);
+  b = make_float4(p2.x, p2.y, p3.x, p3.y);
+}
+template <>
+__device__ __forceinline__ void widen8<float>(const uint4&, float4&, float4&) {}
+
+template <typename T>
+__device__ __forceinline__ T from_float(float f);
+template <>
+__device__ __forceinline__ float from_float<float>(float f) { return f; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float f) { return __float2bfloat16_rn(f); }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float f) { return __float2half_rn(f); }
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+
+}  // namespace ssw

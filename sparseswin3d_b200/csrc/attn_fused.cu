@@ -23,10 +23,11 @@
 // Every wait is a bounded poll of an mbarrier; on expiry the kernel sets SSW_DEV_TIMEOUT in the
 // plan header and every thread leaves through the same exit.
 #include <math.h>
+#include <stdlib.h>
 
 #include <type_traits>
 
-#include "ssw_common.cuh"
+#include "attn_common.cuh"
 
 namespace ssw {
 
@@ -57,7 +58,6 @@ struct AttnParams {
   int table_floats;   // > 0: the bias table is staged in shared memory (that many floats)
 };
 
-constexpr float kLog2e = 1.4426950408889634f;
 
 // Shared memory: [barriers 256 B][bias table][stage 0][stage 1]...
 // Stage: [desc int4][vox int[kMaxTile]][rows tile*row_stride][16-bit out staging]
@@ -68,76 +68,6 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kBarBytes = 256;
 constexpr int kStageVoxOff = 16;
 constexpr int kStageRowsOff = kStageVoxOff + kMaxTile * 4;
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// shared -> global bulk (TMA) store of `bytes` (multiple of 16, both addresses 16-byte aligned)
-__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// make generic-proxy writes to shared memory visible to the async proxy (bulk stores)
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// Barrier among the warps of one consumer group, built on an mbarrier so that the wait is bounded.
-__device__ __forceinline__ bool group_barrier(uint64_t* bar, uint32_t& phase, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-  const bool ok = mbar_wait_bounded(bar, phase);
-  phase ^= 1;
-  return ok;
-}
-
-template <typename T>
-__device__ __forceinline__ void widen8(const uint4& u, float4& a, float4& b);
-template <>
-__device__ __forceinline__ void widen8<__nv_bfloat16>(const uint4& u, float4& a, float4& b) {
-  a = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
-                  __uint_as_float(u.y & 0xffff0000u));
-  b = make_float4(__uint_as_float(u.z << 16), __uint_as_float(u.z & 0xffff0000u), __uint_as_float(u.w << 16),
-                  __uint_as_float(u.w & 0xffff0000u));
-}
-template <>
-__device__ __forceinline__ void widen8<__half>(const uint4& u, float4& a, float4& b) {
-  float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
-  float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
-  float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&u.z));
-  float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&u.w));
-  a = make_float4(p0.x, p0.y, p1.x, p1.y);
-  b = make_float4(p2.x, p2.y, p3.x, p3.y);
-}
-template <>
-__device__ __forceinline__ void widen8<float>(const uint4&, float4&, float4&) {}
-
-template <typename T>
-__device__ __forceinline__ T from_float(float f);
-template <>
-__device__ __forceinline__ float from_float<float>(float f) { return f; }
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float f) { return __float2bfloat16_rn(f); }
-template <>
-__device__ __forceinline__ __half from_float<__half>(float f) { return __float2half_rn(f); }
-
-template <typename T>
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  } else {
-    __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-  }
-}
 
 // Online-softmax state of one (query row, head).
 template <int HD>
@@ -359,8 +289,6 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   constexpr bool kHalf = sizeof(T) == 2;
   const int tile = p.tile, C = p.C, H = p.H;
   const int S = p.stages, G = p.groups;
-  const int n_small = p.header[SSW_H_PACKS_SMALL];
-  const int n_items = p.header[SSW_H_PACKS];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);   // [kMaxStages] data landed
   uint64_t* empty = full + kMaxStages;                   // [kMaxStages] stage may be refilled
   uint64_t* done = empty + kMaxStages;                   // [kMaxStages] group finished computing
@@ -392,8 +320,13 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     mbar_init(bbar, 1);
     mbar_fence_init();
   }
+  // Only the barrier set-up may run ahead of the kernel this launch is chained behind: the plan,
+  // qkv and the bias table may all have been written by it.
+  grid_dependency_wait();
   if constexpr (kTableSmem)
     for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) table_s[i] = __ldg(p.table + i) * kLog2e;
+  const int n_small = p.header[SSW_H_PACKS_SMALL];
+  const int n_items = p.header[SSW_H_PACKS];
   __syncthreads();
 
   // ------------------------------------------------------------------------------------------
@@ -674,6 +607,15 @@ static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, cons
   if (groups > kMaxGroups) groups = kMaxGroups;
   while (groups > 1 && groups * s.group_threads + 32 > 1024) --groups;
   if (groups < 1) groups = 1;
+  // Tuning overrides (experiments only): SSW_STAGES / SSW_GROUPS within the shared-memory budget.
+  if (const char* e = getenv("SSW_STAGES")) {
+    const int v = atoi(e);
+    if (v >= 2 && v <= stages) s.stages = stages = v;
+  }
+  if (const char* e = getenv("SSW_GROUPS")) {
+    const int v = atoi(e);
+    if (v >= 1 && v <= kMaxGroups && v <= stages && v * s.group_threads + 32 <= 1024) groups = v;
+  }
   s.groups = groups;
   s.smem = fixed + (size_t)(stages > 0 ? stages : 1) * s.stage_bytes;
   return s;
@@ -687,15 +629,15 @@ static int launch_attn(const AttnParams& p, int threads, size_t smem, cudaStream
   if (threads <= 384) {
     auto kern = k_attn_fused<T, HD, kTableSmem, 384>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<sms, threads, smem, stream>>>(p);
+    SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), smem, stream, p));
   } else if (threads <= 512) {
     auto kern = k_attn_fused<T, HD, kTableSmem, 512>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<sms, threads, smem, stream>>>(p);
+    SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), smem, stream, p));
   } else {
     auto kern = k_attn_fused<T, HD, kTableSmem, 1024>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<sms, threads, smem, stream>>>(p);
+    SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), smem, stream, p));
   }
   SSW_LAUNCH_CHECK("k_attn_fused");
   return SSW_OK;

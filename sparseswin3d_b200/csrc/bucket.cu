@@ -76,6 +76,7 @@ __global__ void k_window_keys(KeySrc s, int64_t n, int32_t* __restrict__ indices
 
 __global__ void k_count(KeySrc s, int64_t n, int words, int32_t* __restrict__ count, uint32_t* __restrict__ bitmap,
                         int32_t* __restrict__ header) {
+  grid_dependency_wait();
   int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (v >= n) return;
   int w, pos, r;
@@ -135,6 +136,7 @@ __device__ Tri block_excl_scan(Tri v, Tri& total) {
 __global__ void __launch_bounds__(kScanThreads) k_reduce(const int32_t* __restrict__ count, int n_windows,
                                                          int32_t* __restrict__ partials, int32_t* __restrict__ header,
                                                          int n_blocks) {
+  grid_dependency_wait();
   int base = blockIdx.x * kScanBlock + threadIdx.x * kScanItems;
   Tri t{0, 0, 0ull};
 #pragma unroll
@@ -193,6 +195,7 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
   extern __shared__ int32_t hist[];  // n_per_window + 2
   BinTables bins(bins_base, n_per_window);
   for (int i = threadIdx.x; i < n_per_window + 2; i += blockDim.x) hist[i] = 0;
+  grid_dependency_wait();
   __syncthreads();
   int base = blockIdx.x * kScanBlock + threadIdx.x * kScanItems;
   int c[kScanItems];
@@ -287,6 +290,7 @@ __global__ void k_order(const int32_t* __restrict__ header, const int32_t* __res
                         int32_t* __restrict__ pack_desc, int32_t* __restrict__ bins_base, int n_per_window, int tile,
                         int w_blocks) {
   BinTables bins(bins_base, n_per_window);
+  grid_dependency_wait();
   if ((int)blockIdx.x < w_blocks) {
     int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= header[SSW_H_W]) return;
@@ -326,9 +330,10 @@ __global__ void k_scatter(KeySrc s, int64_t n, int words, const int32_t* __restr
                           int32_t* __restrict__ inv_perm, int32_t* __restrict__ pack_perm,
                           int32_t* __restrict__ pack_meta) {
   int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (v >= n) return;
-  int w, pos, r;
-  if (!load_key(s, v, w, pos, r)) return;
+  int w = 0, pos = 0, r = 0;
+  const bool ok = v < n && load_key(s, v, w, pos, r);  // coordinates are an input, not a product of the chain
+  grid_dependency_wait();
+  if (!ok) return;
   int k = compact[w];
   if (k < 0) return;
   const uint32_t* bm = bitmap + (int64_t)w * words;
@@ -493,25 +498,26 @@ extern "C" int ssw_bucket_windows(const int32_t* coords, const ssw_geometry* geo
   uint32_t* bitmap = reinterpret_cast<uint32_t*>(scratch + L->off_bitmap);
   int32_t* partials = scratch + L->off_partials;
   const unsigned vox_blocks = (unsigned)ceil_div64(N, 256);
+  // first of the chain: ordinary launch, fully ordered behind the clears and the caller's earlier work
   k_count<<<vox_blocks, 256, 0, stream>>>(s, N, L->bitmap_words, count, bitmap, header);
   SSW_LAUNCH_CHECK("k_count");
   const int blocks = (int)ceil_div64(L->n_windows, kScanBlock);
-  k_reduce<<<blocks, kScanThreads, 0, stream>>>(count, L->n_windows, partials, header, blocks);
-  SSW_LAUNCH_CHECK("k_reduce");
-  k_compact<<<blocks, kScanThreads, sizeof(int32_t) * (n + 2), stream>>>(
-      count, L->n_windows, partials, header, plan + L->off_win_id, plan + L->off_win_start, plan + L->off_coo_start,
-      plan + L->off_bins, n, L->tile_rows, blocks);
-  SSW_LAUNCH_CHECK("k_compact");
+  SSW_CUDA_TRY(launch_chained(k_reduce, dim3(blocks), dim3(kScanThreads), 0, stream, (const int32_t*)count,
+                              (int)L->n_windows, partials, header, blocks));
+  SSW_CUDA_TRY(launch_chained(k_compact, dim3(blocks), dim3(kScanThreads), sizeof(int32_t) * (n + 2), stream, count,
+                              (int)L->n_windows, (const int32_t*)partials, header, plan + L->off_win_id,
+                              plan + L->off_win_start, plan + L->off_coo_start, plan + L->off_bins, n,
+                              (int)L->tile_rows, blocks));
   const int w_blocks = (int)ceil_div64(L->w_cap, 256);
   const int p_blocks = (int)ceil_div64(L->pack_cap, 256);
-  k_order<<<w_blocks + p_blocks, 256, 0, stream>>>(header, plan + L->off_win_start, plan + L->off_win_pstart,
-                                                   plan + L->off_pack_win, plan + L->off_pack_desc,
-                                                   plan + L->off_bins, n, L->tile_rows, w_blocks);
-  SSW_LAUNCH_CHECK("k_order");
-  k_scatter<<<vox_blocks, 256, 0, stream>>>(s, N, L->bitmap_words, count, bitmap, plan + L->off_win_start,
-                                            plan + L->off_win_pstart, plan + L->off_perm, plan + L->off_inv_perm,
-                                            plan + L->off_pack_perm, plan + L->off_pack_meta);
-  SSW_LAUNCH_CHECK("k_scatter");
+  SSW_CUDA_TRY(launch_chained(k_order, dim3(w_blocks + p_blocks), dim3(256), 0, stream, (const int32_t*)header,
+                              (const int32_t*)(plan + L->off_win_start), plan + L->off_win_pstart,
+                              plan + L->off_pack_win, plan + L->off_pack_desc, plan + L->off_bins, n,
+                              (int)L->tile_rows, w_blocks));
+  SSW_CUDA_TRY(launch_chained(k_scatter, dim3(vox_blocks), dim3(256), 0, stream, s, N, (int)L->bitmap_words,
+                              (const int32_t*)count, (const uint32_t*)bitmap, (const int32_t*)(plan + L->off_win_start),
+                              (const int32_t*)(plan + L->off_win_pstart), plan + L->off_perm, plan + L->off_inv_perm,
+                              plan + L->off_pack_perm, plan + L->off_pack_meta));
   return SSW_OK;
 }
 

@@ -75,6 +75,30 @@ __host__ __device__ inline int packs_of_bin(int c, int cnt, int tile) {
 }
 
 #ifdef __CUDACC__
+// ---- programmatic dependent launch ------------------------------------------------------------
+// Kernels of one call are chained with programmatic stream serialization: a kernel may be
+// scheduled while its predecessor drains, runs whatever does not depend on the predecessor, and
+// calls grid_dependency_wait() before it touches anything the predecessor wrote.  Every kernel
+// calls it, so completion is transitive along the chain.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                         Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ---- warp / block primitives ------------------------------------------------------------
 __device__ __forceinline__ int warp_incl_scan(int v) {
 #pragma unroll
