@@ -140,18 +140,20 @@ def run_ours(args):
     qkv = [q.to(dev) for q in qkv_h]
     outs = [torch.empty(N_VOX, C, dtype=dtype, device=dev) for _ in range(n_sets)]
     geoms = [window.resolve_geometry(1, dims, WINDOW, (0, 0, 0)), window.resolve_geometry(1, dims, WINDOW, SHIFT)]
-    tile = args.tile or attention.default_tile_rows(HEADS, HEAD_DIM, dtype, WINDOW)
+    pp = attention.plan_params(HEADS, HEAD_DIM, dtype, WINDOW)
+    tile = args.tile or pp["tile_rows"]
+    padded = int(pp["padded"])
     scale = HEAD_DIM ** -0.5
     scratch = torch.empty(1, dtype=torch.int32, device=dev)
 
     def one_pass(i, g, q, o):
         nonlocal scratch
-        plan = window.bucket_windows(coords=coords, geom=g, rpb_window=WINDOW, tile_rows=tile, scratch=scratch)
+        plan = window.bucket_windows(coords=coords, geom=g, rpb_window=WINDOW, tile_rows=tile, padded=bool(padded), scratch=scratch)
         attention.window_attention_fused(q, plan, table, scale, use_mask=bool(g.shifted), out=o)
         return plan
 
     L = _lib.PlanLayout()
-    _lib.check(_lib.lib.ssw_plan_layout_init(L, N_VOX, geoms[0].n_windows, geoms[0].n_per_window, tile), "layout")
+    _lib.check(_lib.lib.ssw_plan_layout_init(L, N_VOX, geoms[0].n_windows, geoms[0].n_per_window, tile, padded), "layout")
     scratch = torch.empty(L.scratch_ints, dtype=torch.int32, device=dev)
 
     def step(s):
@@ -217,7 +219,7 @@ def run_ours(args):
     value = 2.0 * N_VOX * world * args.steps / (ms * 1e-3)
 
     # ---- dominant kernel alone: graphs of `reps` back-to-back k_attn_fused launches ----------
-    plans = [window.bucket_windows(coords=coords, geom=g, rpb_window=WINDOW, tile_rows=tile) for g in geoms]
+    plans = [window.bucket_windows(coords=coords, geom=g, rpb_window=WINDOW, tile_rows=tile, padded=bool(padded)) for g in geoms]
     torch.cuda.synchronize()
     reps = 12
 
@@ -228,7 +230,7 @@ def run_ours(args):
 
     def bucket_only(_):
         for i in range(reps):
-            window.bucket_windows(coords=coords, geom=geoms[i % 2], rpb_window=WINDOW, tile_rows=tile, scratch=scratch)
+            window.bucket_windows(coords=coords, geom=geoms[i % 2], rpb_window=WINDOW, tile_rows=tile, padded=bool(padded), scratch=scratch)
 
     def time_graph(fn):
         g = capture(fn, 1)[0]
@@ -260,7 +262,7 @@ def run_ours(args):
         c_d.copy_(coords_h, non_blocking=True)
         q_d.copy_(qkv_h[s], non_blocking=True)
         for g in geoms:
-            plan = window.bucket_windows(coords=c_d, geom=g, rpb_window=WINDOW, tile_rows=tile, scratch=scratch)
+            plan = window.bucket_windows(coords=c_d, geom=g, rpb_window=WINDOW, tile_rows=tile, padded=bool(padded), scratch=scratch)
             o = attention.window_attention_fused(q_d, plan, table, scale, use_mask=bool(g.shifted), out=outs[s])
             out_h[s].copy_(o, non_blocking=True)
 

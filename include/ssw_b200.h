@@ -93,7 +93,8 @@ enum {
   SSW_H_TILE = 7,     /* tile_rows the plan was built for                              */
   SSW_H_TICKET_A = 8, /* internal                                                      */
   SSW_H_TICKET_B = 9, /* internal                                                      */
-  SSW_H_PACKS_SMALL = 10 /* leading work items that are packs of windows with c <= tile */
+  SSW_H_PACKS_SMALL = 10, /* leading work items that are packs of windows with c <= tile */
+  SSW_H_PADDED = 11   /* 1: packs give every window a padded run of row slots (tensor-core kernel) */
 };
 
 typedef struct ssw_plan_layout {
@@ -104,6 +105,8 @@ typedef struct ssw_plan_layout {
   int32_t w_cap;        /* capacity for non-empty windows = min(n_vox, n_windows)       */
   int32_t pack_cap;     /* upper bound of fused-kernel work items                       */
   int32_t bitmap_words; /* ceil(n_per_window / 32)                                      */
+  int32_t padded;       /* packs pad windows to 1,2,4,8,16,32,.. row slots (16-bit inputs)   */
+  int32_t reserved_;    /* keeps the 64-bit members aligned                             */
   /* offsets into `plan`, in int32 units */
   int64_t off_header;   /* [SSW_HEADER_INTS]                                            */
   int64_t off_perm;     /* [N]   sorted row (window,pos order) -> voxel                 */
@@ -125,12 +128,16 @@ typedef struct ssw_plan_layout {
   int64_t scratch_ints;
 } ssw_plan_layout;
 
-/* Host only.  tile_rows in 1..64; 0 means 64. */
+/* Host only.  tile_rows in 1..64 (0 means 64).  padded != 0 builds the work list for the
+ * tensor-core kernel that serves 16-bit inputs (tile_rows then a multiple of 16); take both values
+ * from ssw_default_tile_rows / ssw_default_padded for the configuration. */
 int ssw_plan_layout_init(ssw_plan_layout* L, int64_t n_vox, int32_t n_windows, int32_t n_per_window,
-                         int32_t tile_rows);
+                         int32_t tile_rows, int32_t padded);
 /* The default tile_rows for a configuration (host only): the largest tile whose two pipeline
  * stages, plus the bias table when it is small enough to stage, let two CTAs share an SM. */
 int32_t ssw_default_tile_rows(int32_t heads, int32_t head_dim, int dtype, const int32_t rpb_window[3]);
+/* 1 when ssw_attn_fused serves this dtype with the tensor-core kernel (bf16, fp16), else 0. */
+int32_t ssw_default_padded(int dtype);
 
 /* Key source of ssw_bucket_windows: exactly one of `coords` (with `geom`) or `indices` is
  * non-NULL.  With `indices` ([N,2] int32, the layout window_partition_sparse leaves in

@@ -15,6 +15,7 @@ SSW_OK = 0
 SSW_F32, SSW_BF16, SSW_F16 = 0, 1, 2
 HEADER_INTS = 64
 H_N, H_W, H_PACKS, H_ERROR, H_CMAX, H_SUMC2_LO, H_SUMC2_HI, H_TILE = range(8)
+H_PACKS_SMALL, H_PADDED = 10, 11
 DEV_BAD_COORD, DEV_DUPLICATE, DEV_COO_RANGE, DEV_TIMEOUT = 1, 2, 4, 8
 
 i32, i64, vp, f32 = C.c_int32, C.c_int64, C.c_void_p, C.c_float
@@ -28,7 +29,7 @@ class Geometry(C.Structure):
 
 class PlanLayout(C.Structure):
     _fields_ = [("n_vox", i64), ("n_windows", i32), ("n_per_window", i32), ("tile_rows", i32), ("w_cap", i32),
-                ("pack_cap", i32), ("bitmap_words", i32),
+                ("pack_cap", i32), ("bitmap_words", i32), ("padded", i32), ("reserved_", i32),
                 ("off_header", i64), ("off_perm", i64), ("off_inv_perm", i64), ("off_win_id", i64),
                 ("off_win_start", i64), ("off_coo_start", i64), ("off_win_pstart", i64), ("off_pack_win", i64),
                 ("off_pack_perm", i64), ("off_pack_meta", i64), ("off_pack_desc", i64), ("off_bins", i64),
@@ -54,7 +55,8 @@ def _load() -> C.CDLL:
         "ssw_geometry_resolve": (C.c_int, [P(Geometry)]),
         "ssw_window_keys": (C.c_int, [vp, i64, P(Geometry), vp, vp, vp, vp]),
         "ssw_default_tile_rows": (i32, [i32, i32, C.c_int, P(i32)]),
-        "ssw_plan_layout_init": (C.c_int, [P(PlanLayout), i64, i32, i32, i32]),
+        "ssw_plan_layout_init": (C.c_int, [P(PlanLayout), i64, i32, i32, i32, i32]),
+        "ssw_default_padded": (i32, [C.c_int]),
         "ssw_bucket_windows": (C.c_int, [vp, P(Geometry), vp, vp, i32, P(i32), P(PlanLayout), vp, vp, vp]),
         "ssw_bucket_windows_static_capacity": (i64, []),
         "ssw_bucket_windows_static": (C.c_int, [vp, P(Geometry), vp, vp, i32, P(i32), P(PlanLayout), vp, vp]),

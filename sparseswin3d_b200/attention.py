@@ -38,6 +38,10 @@ def window_attention_fused(qkv: torch.Tensor, plan: WindowPlan, table: torch.Ten
     N, _, H, hd = qkv.shape
     if N != plan.layout.n_vox:
         raise _lib.SswError(f"plan was built for {plan.layout.n_vox} voxels, qkv has {N}")
+    want_padded = bool(lib.ssw_default_padded(dtype_code(qkv.dtype))) and not return_attn
+    if bool(plan.layout.padded) and not want_padded:
+        raise _lib.SswError("this plan was built with padded=True (tensor-core work list); fp32 tensors and "
+                            "return_attn=True need a plan built with padded=False")
     if use_mask and not plan.has_regions:
         raise _lib.SswError("use_mask=True but the plan carries no region ids (no shift / no mask given)")
     table = table.detach()
@@ -59,6 +63,14 @@ def window_attention_fused(qkv: torch.Tensor, plan: WindowPlan, table: torch.Ten
                              float(scale), int(bool(use_mask)), ptr(out), ptr(attn), stream_ptr(qkv.device)),
           "ssw_attn_fused")
     return (out, attn) if return_attn else out
+
+
+def plan_params(num_heads: int, head_dim: int, dtype: torch.dtype, rpb_window: Sequence[int] = (7, 7, 7)) -> dict:
+    """Keyword arguments for bucket_windows that match the kernel ssw_attn_fused runs for this
+    configuration: fp32 -> CUDA-core kernel, contiguous packs; bf16/fp16 -> tensor-core kernel,
+    padded packs."""
+    return {"tile_rows": default_tile_rows(num_heads, head_dim, dtype, rpb_window),
+            "padded": bool(lib.ssw_default_padded(dtype_code(dtype))), "rpb_window": tuple(int(x) for x in rpb_window)}
 
 
 class WindowAttentionSparse(nn.Module):
@@ -102,7 +114,8 @@ class WindowAttentionSparse(nn.Module):
 
     def plan(self, x, mask: Optional[torch.Tensor], dtype: torch.dtype) -> WindowPlan:
         return bucket_windows(indices=x.indices, n_windows=int(x.batch_size), n_per_window=int(x.spatial_shape[0]),
-                              mask=mask, rpb_window=self.window_size, tile_rows=self.tile_rows(dtype))
+                              mask=mask, **plan_params(self.num_heads, self.dim // self.num_heads, dtype,
+                                                       self.window_size))
 
     @torch.no_grad()
     def forward_features(self, features: torch.Tensor, plan: WindowPlan, use_mask: bool) -> torch.Tensor:

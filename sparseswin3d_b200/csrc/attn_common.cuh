@@ -10,6 +10,36 @@ namespace ssw {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
+constexpr int kMaxStages = 6;
+constexpr int kMaxGroups = 4;
+constexpr int kMaxTile = 64;
+
+struct AttnParams {
+  const void* qkv;
+  void* out;
+  void* attn_vals;
+  int32_t* header;
+  const int4* pack_desc;
+  const int32_t* pack_perm;
+  const int32_t* pack_meta;
+  const int32_t* pack_win;
+  const int32_t* coo_start;
+  const float* table;
+  int rel_off;
+  int H, C, tile, HG;
+  int group_threads;  // threads of one consumer group (multiple of 32) = ceil32(tile * HG)
+  int groups, stages;
+  float scale;
+  int use_mask;
+  int row_stride;     // bytes between fp32 rows in a stage
+  int stage_bytes;    // bytes of one pipeline stage
+  int out_off;        // byte offset of the 16-bit output staging area inside a stage (0 for fp32)
+  int table_floats;   // > 0: the bias table is staged in shared memory (that many floats)
+  int skip_packs;     // CUDA-core kernel only: leave the packs to the tensor-core kernel
+};
+
+
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -31,34 +31,6 @@
 
 namespace ssw {
 
-constexpr int kMaxStages = 6;
-constexpr int kMaxGroups = 4;
-constexpr int kMaxTile = 64;
-
-struct AttnParams {
-  const void* qkv;
-  void* out;
-  void* attn_vals;
-  int32_t* header;
-  const int4* pack_desc;
-  const int32_t* pack_perm;
-  const int32_t* pack_meta;
-  const int32_t* pack_win;
-  const int32_t* coo_start;
-  const float* table;
-  int rel_off;
-  int H, C, tile, HG;
-  int group_threads;  // threads of one consumer group (multiple of 32) = ceil32(tile * HG)
-  int groups, stages;
-  float scale;
-  int use_mask;
-  int row_stride;     // bytes between fp32 rows in a stage
-  int stage_bytes;    // bytes of one pipeline stage
-  int out_off;        // byte offset of the 16-bit output staging area inside a stage (0 for fp32)
-  int table_floats;   // > 0: the bias table is staged in shared memory (that many floats)
-};
-
-
 // Shared memory: [barriers 256 B][bias table][stage 0][stage 1]...
 // Stage: [desc int4][vox int[kMaxTile]][rows tile*row_stride][16-bit out staging]
 // Row:   [q | k | v as 3*C floats][meta int2 {byte offset of the key's bias-table row,
@@ -323,16 +295,18 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   // Only the barrier set-up may run ahead of the kernel this launch is chained behind: the plan,
   // qkv and the bias table may all have been written by it.
   grid_dependency_wait();
-  if constexpr (kTableSmem)
-    for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) table_s[i] = __ldg(p.table + i) * kLog2e;
   const int n_small = p.header[SSW_H_PACKS_SMALL];
   const int n_items = p.header[SSW_H_PACKS];
+  if (p.skip_packs && n_items <= n_small) return;  // launched for the large windows only and there are none
+  if constexpr (kTableSmem)
+    for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) table_s[i] = __ldg(p.table + i) * kLog2e;
   __syncthreads();
 
   // ------------------------------------------------------------------------------------------
   // Phase A: packs, producer / consumer pipeline
   // ------------------------------------------------------------------------------------------
-  const int my_items = n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int my_items =
+      (!p.skip_packs && n_small > (int)blockIdx.x) ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   bool timed_out = false;
   if (is_producer) {
     // register pipeline: descriptor of item i+1, voxel ids / metadata of item i
@@ -653,12 +627,18 @@ static int dispatch(const AttnParams& p, int hd, int threads, size_t smem, cudaS
   return SSW_E_UNSUPPORTED;
 }
 
+int mma_default_tile(int heads, int head_dim, const int32_t rpb_window[3]);
+int run_attn_mma(AttnParams p, int dtype, int head_dim, const int32_t rpb_window[3], cudaStream_t stream);
+
 }  // namespace ssw
 
 using namespace ssw;
 
+extern "C" int32_t ssw_default_padded(int dtype) { return dtype == SSW_BF16 || dtype == SSW_F16; }
+
 extern "C" int32_t ssw_default_tile_rows(int32_t heads, int32_t head_dim, int dtype, const int32_t rpb_window[3]) {
   if (heads <= 0 || head_dim <= 0 || !rpb_window) return 0;
+  if (ssw_default_padded(dtype)) return mma_default_tile(heads, head_dim, rpb_window);
   const int elt = dtype == SSW_F32 ? 4 : 2;
   // the largest tile that still leaves three pipeline stages
   static const int kTiles[] = {64, 48, 32, 24, 16};
@@ -709,7 +689,15 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   p.stage_bytes = s.stage_bytes;
   p.out_off = s.out_off;
   p.table_floats = s.table_floats;
+  p.skip_packs = 0;
   cudaStream_t stream = (cudaStream_t)stream_;
+  if (L->padded) {
+    // padded plan: the packs go to the tensor-core kernel, windows beyond a pack to phase B below
+    if (elt != 2 || attn_vals) return SSW_E_INVALID;
+    const int rc = run_attn_mma(p, dtype, head_dim, rpb_window, stream);
+    if (rc != SSW_OK) return rc;
+    p.skip_packs = 1;
+  }
   switch (dtype) {
     case SSW_F32: return dispatch<float>(p, head_dim, threads, s.smem, stream);
     case SSW_BF16: return dispatch<__nv_bfloat16>(p, head_dim, threads, s.smem, stream);

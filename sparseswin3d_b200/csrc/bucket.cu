@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
                                                           int32_t* __restrict__ header, int32_t* __restrict__ win_id,
                                                           int32_t* __restrict__ win_start,
                                                           int32_t* __restrict__ coo_start, int32_t* __restrict__ bins_base,
-                                                          int n_per_window, int tile, int n_blocks) {
+                                                          int n_per_window, int tile, int padded, int n_blocks) {
   extern __shared__ int32_t hist[];  // n_per_window + 2
   BinTables bins(bins_base, n_per_window);
   for (int i = threadIdx.x; i < n_per_window + 2; i += blockDim.x) hist[i] = 0;
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
   for (int c0 = 0; c0 < n_per_window + 2; c0 += kScanThreads) {
     int cc = c0 + threadIdx.x;
     int cnt = cc < n_per_window + 2 ? __ldcg(bins.cnt + cc) : 0;
-    Tri v{cnt, cnt * cc, (unsigned long long)packs_of_bin(cc, cnt, tile)};
+    Tri v{cnt, cnt * cc, (unsigned long long)packs_of_bin(cc, cnt, tile, padded)};
     Tri tot2;
     Tri e2 = block_excl_scan(v, tot2);
     e2 = tri_add(e2, carry);
@@ -279,6 +279,7 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
     header[SSW_H_PACKS] = (int)carry.sq;
     if (tile + 1 > n_per_window + 1) header[SSW_H_PACKS_SMALL] = (int)carry.sq;
     header[SSW_H_TILE] = tile;
+    header[SSW_H_PADDED] = padded;
     if (sq >= (1ull << 31)) atomicOr(reinterpret_cast<unsigned*>(header + SSW_H_ERROR), SSW_DEV_COO_RANGE);
   }
 }
@@ -288,7 +289,7 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
 __global__ void k_order(const int32_t* __restrict__ header, const int32_t* __restrict__ win_start,
                         int32_t* __restrict__ win_pstart, int32_t* __restrict__ pack_win,
                         int32_t* __restrict__ pack_desc, int32_t* __restrict__ bins_base, int n_per_window, int tile,
-                        int w_blocks) {
+                        int padded, int w_blocks) {
   BinTables bins(bins_base, n_per_window);
   grid_dependency_wait();
   if ((int)blockIdx.x < w_blocks) {
@@ -313,7 +314,7 @@ __global__ void k_order(const int32_t* __restrict__ header, const int32_t* __res
   int cnt = bins.cnt[c];
   int4 d;
   if (c <= tile) {
-    int wpp = tile / c;
+    int wpp = windows_per_pack(c, tile, padded);
     int first = q * wpp;
     d = make_int4(bins.rowstart[c] + first * c, c, min(wpp, cnt - first), bins.wstart[c] + first);
   } else {
@@ -427,16 +428,18 @@ extern "C" int ssw_window_keys(const int32_t* coords, int64_t n_vox, const ssw_g
 }
 
 extern "C" int ssw_plan_layout_init(ssw_plan_layout* L, int64_t n_vox, int32_t n_windows, int32_t n_per_window,
-                                    int32_t tile_rows) {
+                                    int32_t tile_rows, int32_t padded) {
   if (!L || n_vox < 0 || n_windows <= 0 || n_per_window <= 0) return SSW_E_INVALID;
   if (n_per_window > kMaxPerWindow) return SSW_E_UNSUPPORTED;
   if (n_vox >= (int64_t(1) << 31) - 4096) return SSW_E_RANGE;
   if (tile_rows <= 0) tile_rows = 64;
   if (tile_rows > 64) return SSW_E_INVALID;
+  if (padded && (tile_rows & 15)) return SSW_E_INVALID;
   L->n_vox = n_vox;
   L->n_windows = n_windows;
   L->n_per_window = n_per_window;
   L->tile_rows = tile_rows;
+  L->padded = padded ? 1 : 0;
   L->w_cap = (int32_t)(n_vox < n_windows ? n_vox : n_windows);
   if (L->w_cap < 1) L->w_cap = 1;
   int64_t pack_cap = 2 * ceil_div64(n_vox, tile_rows) + n_per_window + 2;
@@ -507,13 +510,13 @@ extern "C" int ssw_bucket_windows(const int32_t* coords, const ssw_geometry* geo
   SSW_CUDA_TRY(launch_chained(k_compact, dim3(blocks), dim3(kScanThreads), sizeof(int32_t) * (n + 2), stream, count,
                               (int)L->n_windows, (const int32_t*)partials, header, plan + L->off_win_id,
                               plan + L->off_win_start, plan + L->off_coo_start, plan + L->off_bins, n,
-                              (int)L->tile_rows, blocks));
+                              (int)L->tile_rows, (int)L->padded, blocks));
   const int w_blocks = (int)ceil_div64(L->w_cap, 256);
   const int p_blocks = (int)ceil_div64(L->pack_cap, 256);
   SSW_CUDA_TRY(launch_chained(k_order, dim3(w_blocks + p_blocks), dim3(256), 0, stream, (const int32_t*)header,
                               (const int32_t*)(plan + L->off_win_start), plan + L->off_win_pstart,
                               plan + L->off_pack_win, plan + L->off_pack_desc, plan + L->off_bins, n,
-                              (int)L->tile_rows, w_blocks));
+                              (int)L->tile_rows, (int)L->padded, w_blocks));
   SSW_CUDA_TRY(launch_chained(k_scatter, dim3(vox_blocks), dim3(256), 0, stream, s, N, (int)L->bitmap_words,
                               (const int32_t*)count, (const uint32_t*)bitmap, (const int32_t*)(plan + L->off_win_start),
                               (const int32_t*)(plan + L->off_win_pstart), plan + L->off_perm, plan + L->off_inv_perm,

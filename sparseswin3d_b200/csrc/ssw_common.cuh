@@ -64,11 +64,25 @@ struct BinTables {
   }
 };
 
+// Row slots a window of occupancy c takes inside a pack.  Contiguous plans (CUDA-core kernel) use
+// exactly c.  Padded plans (tensor-core kernel) round c up to a power of two below 16 and to a
+// multiple of 16 above, so that 16-row MMA tiles never straddle windows of different position.
+__host__ __device__ inline int slots_of_window(int c, int padded) {
+  if (!padded) return c;
+  if (c > 16) return (c + 15) & ~15;
+  int s = 1;
+  while (s < c) s <<= 1;
+  return s;
+}
+__host__ __device__ inline int windows_per_pack(int c, int tile, int padded) {
+  const int w = tile / slots_of_window(c, padded);
+  return w > 0 ? w : 1;
+}
 // Work items a bin of `cnt` windows with occupancy c needs when one item holds `tile` rows.
-__host__ __device__ inline int packs_of_bin(int c, int cnt, int tile) {
+__host__ __device__ inline int packs_of_bin(int c, int cnt, int tile, int padded) {
   if (cnt == 0 || c == 0) return 0;
   if (c <= tile) {
-    int wpp = tile / c;
+    int wpp = windows_per_pack(c, tile, padded);
     return (cnt + wpp - 1) / wpp;
   }
   return cnt * ((c + tile - 1) / tile);

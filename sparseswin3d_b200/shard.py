@@ -94,15 +94,15 @@ def sharded_window_attention(coords: torch.Tensor, qkv: torch.Tensor, geom, tabl
     from . import attention, window
 
     H, hd = qkv.shape[2], qkv.shape[3]
-    tile = attention.default_tile_rows(H, hd, qkv.dtype, rpb_window)
-    full = window.bucket_windows(coords=coords, geom=geom, rpb_window=rpb_window, tile_rows=tile)
+    pp = attention.plan_params(H, hd, qkv.dtype, rpb_window)
+    full = window.bucket_windows(coords=coords, geom=geom, **pp)
     counts = full.occupancy()
     cuts = window_range_cuts(counts, world, alpha)
     ids = voxels_of_range(full.perm, full.win_start, cuts[rank], cuts[rank + 1])
     if ids.numel():
         sub_coords = coords.index_select(0, ids).contiguous()
         sub_qkv = qkv.index_select(0, ids).contiguous()
-        plan = window.bucket_windows(coords=sub_coords, geom=geom, rpb_window=rpb_window, tile_rows=tile)
+        plan = window.bucket_windows(coords=sub_coords, geom=geom, **pp)
         local = attention.window_attention_fused(sub_qkv, plan, table, scale, use_mask=bool(geom.shifted))
     else:
         local = torch.empty((0, H * hd), dtype=qkv.dtype, device=qkv.device)

@@ -124,14 +124,17 @@ class WindowPlan:
 def bucket_windows(*, coords: Optional[torch.Tensor] = None, geom: Optional[Geometry] = None,
                    indices: Optional[torch.Tensor] = None, n_windows: Optional[int] = None,
                    n_per_window: Optional[int] = None, mask: Optional[torch.Tensor] = None,
-                   rpb_window: Sequence[int] = (7, 7, 7), tile_rows: int = 64,
+                   rpb_window: Sequence[int] = (7, 7, 7), tile_rows: int = 64, padded: bool = False,
                    scratch: Optional[torch.Tensor] = None) -> WindowPlan:
     """Sort voxels by (window, pos) on the device and build the fused kernel's work list.
 
     Give either ``coords`` [N,4] + ``geom`` (pad, cyclic shift, partition and region ids are
     computed on the fly) or ``indices`` [N,2] + ``n_windows`` + ``n_per_window`` (the tensor and
     sizes upstream's WindowAttentionSparse.forward receives as x.indices, x.batch_size,
-    x.spatial_shape[0]) with an optional ``mask`` [nW, n] int8 from compute_mask."""
+    x.spatial_shape[0]) with an optional ``mask`` [nW, n] int8 from compute_mask.
+
+    ``tile_rows`` and ``padded`` shape the fused kernel's work list; take them from
+    ``attention.plan_params(heads, head_dim, dtype, window)`` for the tensor the plan will serve."""
     if (coords is None) == (indices is None):
         raise _lib.SswError("give exactly one of coords= or indices=")
     if coords is not None:
@@ -151,7 +154,7 @@ def bucket_windows(*, coords: Optional[torch.Tensor] = None, geom: Optional[Geom
                 or mask.device != src.device:
             raise _lib.SswError("mask must be a contiguous int8 [nW, n_per_window] tensor on the same device")
     L = PlanLayout()
-    check(lib.ssw_plan_layout_init(L, src.shape[0], int(n_windows), int(n_per_window), int(tile_rows)),
+    check(lib.ssw_plan_layout_init(L, src.shape[0], int(n_windows), int(n_per_window), int(tile_rows), int(bool(padded))),
           "ssw_plan_layout_init")
     dev = src.device
     plan = torch.empty(L.plan_ints, dtype=torch.int32, device=dev)

@@ -65,10 +65,10 @@ def test_geometry_and_layout_reject_bad_sizes():
     with pytest.raises(_lib.SswError):
         W.resolve_geometry(64, (2000, 2000, 2000), (7, 7, 7))  # window table leaves int32
     L = _lib.PlanLayout()
-    assert _lib.lib.ssw_plan_layout_init(L, 1000, 512, 343, 48) == 0
+    assert _lib.lib.ssw_plan_layout_init(L, 1000, 512, 343, 48, 0) == 0
     assert L.w_cap == 512 and L.plan_ints > 4 * 1000 and L.scratch_ints >= 512 * 12
-    assert _lib.lib.ssw_plan_layout_init(L, 1000, 512, 343, 65) != 0
-    assert _lib.lib.ssw_plan_layout_init(L, 2 ** 31, 512, 343, 48) != 0
+    assert _lib.lib.ssw_plan_layout_init(L, 1000, 512, 343, 65, 0) != 0
+    assert _lib.lib.ssw_plan_layout_init(L, 2 ** 31, 512, 343, 48, 0) != 0
     assert _lib.lib.ssw_argsort_workspace_bytes(1000) >= 12000
 
 

@@ -14,13 +14,15 @@ BF16_TOL = 2e-2   # same form, bf16 inputs/outputs against the fp32 oracle
 def _plan(case, dev, dtype, from_coords=True, tile=None):
     from sparseswin3d_b200 import attention, window
 
-    tile = tile or attention.default_tile_rows(case["heads"], case["head_dim"], dtype, case["window"])
+    pp = attention.plan_params(case["heads"], case["head_dim"], dtype, case["window"])
+    if tile:
+        pp["tile_rows"] = tile
     if from_coords:
         g = window.resolve_geometry(case["batch"], case["dims"], case["window"], case["shift"])
-        return window.bucket_windows(coords=case["coords"].to(dev), geom=g, rpb_window=case["window"], tile_rows=tile)
+        return window.bucket_windows(coords=case["coords"].to(dev), geom=g, **pp)
     mask = case["mask"].to(dev) if case["mask"] is not None else None
     return window.bucket_windows(indices=case["indices"].to(dev), n_windows=case["n_windows"], n_per_window=case["n"],
-                                 mask=mask, rpb_window=case["window"], tile_rows=tile)
+                                 mask=mask, **pp)
 
 
 def _check_plan(case, plan):
@@ -92,16 +94,41 @@ def test_fused_half_types(dtype, tol):
     (600, 30, 3, 32, (5, 6, 7)),       # anisotropic window
 ])
 @pytest.mark.parametrize("shift", [False, True])
-def test_fused_shapes(n_vox, grid, heads, hd, window, shift):
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, BF16_TOL), (torch.float16, 3e-3)])
+def test_fused_shapes(n_vox, grid, heads, hd, window, shift, dtype, tol):
+    """fp32 runs the CUDA-core kernel on a contiguous plan, the 16-bit types the tensor-core kernel
+    on a padded plan (windows above one pack fall through to the CUDA-core kernel's second phase)."""
     from sparseswin3d_b200 import attention
 
     dev = torch.device("cuda:0")
     sh = tuple(w // 2 for w in window) if shift else (0, 0, 0)
     case = make_case(n_vox=n_vox, grid=grid, heads=heads, head_dim=hd, window=window, shift=sh, seed=n_vox)
-    plan = _plan(case, dev, torch.float32)
+    plan = _plan(case, dev, dtype)
     _check_plan(case, plan)
-    ref = O.dense_window_attention(case["qkv"], case["indices"], case["scale"], case["table"], case["rpi"], case["mask"])
-    out = attention.window_attention_fused(case["qkv"].to(dev), plan, case["table"].to(dev), case["scale"],
+    qkv = case["qkv"].to(dtype)
+    ref = O.dense_window_attention(qkv.float(), case["indices"], case["scale"], case["table"], case["rpi"], case["mask"])
+    out = attention.window_attention_fused(qkv.to(dev), plan, case["table"].to(dev), case["scale"],
                                            use_mask=case["mask"] is not None)
     assert plan.stats()["error"] == 0
-    assert rel_err(out.cpu(), ref) <= FP32_TOL
+    assert out.dtype == dtype
+    assert rel_err(out.float().cpu(), ref) <= tol
+
+
+def test_padded_plan_is_rejected_for_fp32_and_coo_output():
+    from sparseswin3d_b200 import _lib, attention, window
+
+    dev = torch.device("cuda:0")
+    case = make_case(n_vox=500, grid=20, seed=2)
+    g = window.resolve_geometry(1, case["dims"], case["window"], case["shift"])
+    plan = window.bucket_windows(coords=case["coords"].to(dev), geom=g, **attention.plan_params(3, 32, torch.bfloat16))
+    assert plan.layout.padded == 1
+    with pytest.raises(_lib.SswError):
+        attention.window_attention_fused(case["qkv"].to(dev), plan, case["table"].to(dev), case["scale"])
+    with pytest.raises(_lib.SswError):
+        attention.window_attention_fused(case["qkv"].to(dev).bfloat16(), plan, case["table"].to(dev), case["scale"],
+                                         return_attn=True)
+    # a contiguous plan still serves 16-bit tensors (CUDA-core kernel, widened in shared memory)
+    plan2 = window.bucket_windows(coords=case["coords"].to(dev), geom=g, **attention.plan_params(3, 32, torch.float32))
+    a = attention.window_attention_fused(case["qkv"].to(dev).bfloat16(), plan, case["table"].to(dev), case["scale"])
+    b = attention.window_attention_fused(case["qkv"].to(dev).bfloat16(), plan2, case["table"].to(dev), case["scale"])
+    assert rel_err(a.float().cpu(), b.float().cpu()) <= BF16_TOL

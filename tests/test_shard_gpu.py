@@ -23,8 +23,7 @@ def _worker(rank, world, port, q):
         geom = window.resolve_geometry(1, case["dims"], case["window"], case["shift"])
         coords, qkv, table = case["coords"].to(dev), case["qkv"].to(dev), case["table"].to(dev)
         out, ids = shard.sharded_window_attention(coords, qkv, geom, table, case["scale"], case["window"], rank, world)
-        tile = attention.default_tile_rows(3, 32, torch.float32, case["window"])
-        plan = window.bucket_windows(coords=coords, geom=geom, rpb_window=case["window"], tile_rows=tile)
+        plan = window.bucket_windows(coords=coords, geom=geom, **attention.plan_params(3, 32, torch.float32, case["window"]))
         ref = attention.window_attention_fused(qkv, plan, table, case["scale"], use_mask=True)
         torch.cuda.synchronize()
         q.put((rank, bool(torch.equal(out, ref)), int(ids.numel())))

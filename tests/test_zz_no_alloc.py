@@ -22,7 +22,7 @@ def _run_static(case, dev, tile, shift):
     geom = W.resolve_geometry(case["batch"], case["dims"], case["window"], shift)
     coords = case["coords"].to(dev)
     L = _lib.PlanLayout()
-    _lib.check(_lib.lib.ssw_plan_layout_init(L, coords.shape[0], geom.n_windows, geom.n_per_window, tile), "layout")
+    _lib.check(_lib.lib.ssw_plan_layout_init(L, coords.shape[0], geom.n_windows, geom.n_per_window, tile, 0), "layout")
     assert L.scratch_ints <= _lib.lib.ssw_bucket_windows_static_capacity()
     plan = torch.empty(L.plan_ints, dtype=torch.int32, device=dev)  # the caller's output buffer
     rw = (_lib.i32 * 3)(*case["window"])
@@ -66,7 +66,7 @@ def test_static_scratch_rejects_oversize():
     dev = torch.device("cuda:0")
     geom = W.resolve_geometry(1, (600, 600, 600), (7, 7, 7))  # 636 k windows x 12 ints: beyond the 16 MiB array
     L = _lib.PlanLayout()
-    _lib.check(_lib.lib.ssw_plan_layout_init(L, 16, geom.n_windows, geom.n_per_window, 48), "layout")
+    _lib.check(_lib.lib.ssw_plan_layout_init(L, 16, geom.n_windows, geom.n_per_window, 48, 0), "layout")
     assert L.scratch_ints > _lib.lib.ssw_bucket_windows_static_capacity()
     plan = torch.empty(L.plan_ints, dtype=torch.int32, device=dev)
     coords = torch.zeros((16, 4), dtype=torch.int32, device=dev)
