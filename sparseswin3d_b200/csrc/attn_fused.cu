@@ -13,9 +13,9 @@
 // query row r for heads hg, hg+HG, ...: q comes from the staged row, the thread walks the keys of
 // its own window with a chunked online softmax in the log2 domain (dot products and the P.V
 // update are packed fp32 FMAs, fma.rn.f32x2), and writes its output slice back into the stage.
-// When the group is done, its first warp streams the finished rows to global memory with bulk
-// (TMA) stores and hands the stage back through `empty`.  16-bit inputs are copied into the upper
-// half of each fp32 row and widened in place once per item.
+// Each thread writes its output slice straight to global memory and the group's warps hand the
+// stage back through `empty`.  16-bit inputs are copied into the upper half of each fp32 row and
+// widened in place once per item.
 //
 // Phase B (windows with c > tile): the same arithmetic, one query tile per item, key tiles
 // streamed through stage 0 without overlap; q and the output go straight through global memory.
@@ -263,8 +263,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   const int S = p.stages, G = p.groups;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);   // [kMaxStages] data landed
   uint64_t* empty = full + kMaxStages;                   // [kMaxStages] stage may be refilled
-  uint64_t* done = empty + kMaxStages;                   // [kMaxStages] group finished computing
-  uint64_t* gbar = done + kMaxStages;                    // [kMaxGroups] group-internal barrier
+  uint64_t* gbar = empty + kMaxStages;                   // [kMaxGroups] group-internal barrier
   uint64_t* bbar = gbar + kMaxGroups;                    // phase B copies
   float* table_s = reinterpret_cast<float*>(smem + kBarBytes);
   unsigned char* stage0 = smem + kBarBytes + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
@@ -285,8 +284,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full + s, 1);
-      mbar_init(empty + s, 1);
-      mbar_init(done + s, gwarps);
+      mbar_init(empty + s, gwarps);  // every warp of the consuming group hands the stage back
     }
     for (int g = 0; g < G; ++g) mbar_init(gbar + g, gwarps);
     mbar_init(bbar, 1);
@@ -298,8 +296,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   const int n_small = p.header[SSW_H_PACKS_SMALL];
   const int n_items = p.header[SSW_H_PACKS];
   if (p.skip_packs && n_items <= n_small) return;  // launched for the large windows only and there are none
-  if constexpr (kTableSmem)
-    for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) table_s[i] = __ldg(p.table + i) * kLog2e;
+  if constexpr (kTableSmem) stage_table(table_s, p.table, p.table_floats);
   __syncthreads();
 
   // ------------------------------------------------------------------------------------------
@@ -309,54 +306,53 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       (!p.skip_packs && n_small > (int)blockIdx.x) ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   bool timed_out = false;
   if (is_producer) {
-    // register pipeline: descriptor of item i+1, voxel ids / metadata of item i
-    int4 d_cur = make_int4(0, 0, 0, 0), d_nxt = make_int4(0, 0, 0, 0);
-    int vox[2] = {0, 0}, km[2] = {0, 0};
-    if (my_items > 0) d_cur = __ldg(p.pack_desc + blockIdx.x);
-    if (my_items > 1) d_nxt = __ldg(p.pack_desc + blockIdx.x + gridDim.x);
-    if (my_items > 0) {
-      const int nr = d_cur.z * d_cur.y;
+    // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
+    // of item i+3 (whose descriptor arrived an iteration ago) are requested while item i is issued,
+    // so no iteration waits on a global load.
+    constexpr int kAhead = 3;
+    int4 dq[kAhead + 2];
+    int vox[kAhead][2], km[kAhead][2];
+    auto fetch = [&](const int4& d, int (&v)[2], int (&m)[2]) {
+      const int nr = d.z * d.y;
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int rr = lane + 32 * k;
+        v[k] = 0;
+        m[k] = 0;
         if (rr < nr) {
-          vox[k] = __ldg(p.pack_perm + d_cur.x + rr);
-          km[k] = __ldg(p.pack_meta + d_cur.x + rr);
+          v[k] = __ldg(p.pack_perm + d.x + rr);
+          m[k] = __ldg(p.pack_meta + d.x + rr);
         }
       }
-    }
+    };
+#pragma unroll
+    for (int a = 0; a <= kAhead + 1; ++a)
+      dq[a] = a < my_items ? __ldg(p.pack_desc + blockIdx.x + (size_t)a * gridDim.x) : make_int4(0, 0, 0, 0);
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) fetch(dq[a], vox[a], km[a]);
     for (int i = 0; i < my_items; ++i) {
       const int s = i % S;
       const int use = i / S;
-      // prefetch for later iterations (nothing in this iteration waits on these loads)
-      int4 d_nn = make_int4(0, 0, 0, 0);
-      if (i + 2 < my_items) d_nn = __ldg(p.pack_desc + blockIdx.x + (size_t)(i + 2) * gridDim.x);
-      int vox_n[2] = {0, 0}, km_n[2] = {0, 0};
-      if (i + 1 < my_items) {
-        const int nr = d_nxt.z * d_nxt.y;
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int rr = lane + 32 * k;
-          if (rr < nr) {
-            vox_n[k] = __ldg(p.pack_perm + d_nxt.x + rr);
-            km_n[k] = __ldg(p.pack_meta + d_nxt.x + rr);
-          }
-        }
-      }
+      const int4 d_new = i + kAhead + 2 < my_items
+                             ? __ldg(p.pack_desc + blockIdx.x + (size_t)(i + kAhead + 2) * gridDim.x)
+                             : make_int4(0, 0, 0, 0);
+      int vox_n[2], km_n[2];
+      fetch(dq[kAhead], vox_n, km_n);  // item i + kAhead (an all-zero descriptor fetches nothing)
       if (use > 0 && !mbar_wait_bounded(empty + s, (use - 1) & 1)) {
         timed_out = true;
         break;
       }
       unsigned char* st = stage0 + (size_t)s * p.stage_bytes;
+      const int4 d_cur = dq[0];
       const int nr = d_cur.z * d_cur.y;
       if (lane == 0) *reinterpret_cast<int4*>(st) = d_cur;
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int rr = lane + 32 * k;
         if (rr < nr) {
-          reinterpret_cast<int*>(st + kStageVoxOff)[rr] = vox[k];
-          *reinterpret_cast<int2*>(st + kStageRowsOff + (size_t)rr * p.row_stride + data_bytes) =
-              make_int2(meta_rel(km[k]) * H * 4, meta_region(km[k]) | ((meta_rel(km[k]) + p.rel_off) << 8));
+          reinterpret_cast<int*>(st + kStageVoxOff)[rr] = vox[0][k];
+          *reinterpret_cast<int2*>(st + kStageRowsOff + (size_t)rr * p.row_stride + data_bytes) = make_int2(
+              meta_rel(km[0][k]) * H * 4, meta_region(km[0][k]) | ((meta_rel(km[0][k]) + p.rel_off) << 8));
         }
       }
       __syncwarp();
@@ -367,14 +363,23 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
         const int rr = lane + 32 * k;
         if (rr < nr)
           bulk_g2s(st + kStageRowsOff + (size_t)rr * p.row_stride + copy_off,
-                   reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[k] * 3 * C, copy_bytes, full + s);
+                   reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[0][k] * 3 * C, copy_bytes, full + s);
       }
-      d_cur = d_nxt;
-      d_nxt = d_nn;
+#pragma unroll
+      for (int a = 0; a <= kAhead; ++a) dq[a] = dq[a + 1];
+      dq[kAhead + 1] = d_new;
+#pragma unroll
+      for (int a = 0; a + 1 < kAhead; ++a) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          vox[a][k] = vox[a + 1][k];
+          km[a][k] = km[a + 1][k];
+        }
+      }
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        vox[k] = vox_n[k];
-        km[k] = km_n[k];
+        vox[kAhead - 1][k] = vox_n[k];
+        km[kAhead - 1][k] = km_n[k];
       }
     }
   } else {
@@ -383,7 +388,6 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     const int hg = ltid / tile;
     const int r = ltid - hg * tile;
     const bool thread_used = hg < p.HG;
-    const bool store_warp = ltid < 32;
     uint32_t gphase = 0;
     RowState<HD> st;
     for (int i = g; i < my_items && !timed_out; i += G) {
@@ -410,6 +414,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       const int kbeg = wl * c;
       if (row_active) {
         unsigned char* myrow = rows + (size_t)r * p.row_stride;
+        const int my_vox = reinterpret_cast<const int*>(sp + kStageVoxOff)[r];
         const int2 me = *reinterpret_cast<const int2*>(myrow + data_bytes);
         const int my_rel = (me.y >> 8) * H;
         const int my_region = me.y & 31;
@@ -428,36 +433,14 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
             attend_keys_m<T, HD, true, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, kbeg, c,
                                                    (C + h * HD) * 4, C, table_h, my_region, inv_l, dst);
           }
-          // fp32: the slice that held my q; 16-bit: the stage's output area
-          T* so = kHalf ? reinterpret_cast<T*>(sp + p.out_off + (size_t)r * out_bytes) + h * HD
-                        : reinterpret_cast<T*>(myrow) + h * HD;
-          store_out<T, HD>(so, st, inv_l);
+          // Straight to global memory: each thread owns a 16-byte-aligned run of HD outputs of one
+          // row (bulk stores of whole rows were tried; one bulk operation per row is what bounds them).
+          store_out<T, HD>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD, st, inv_l);
         }
       }
-      fence_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(done + s);
-      if (store_warp) {
-        if (!mbar_wait_bounded(done + s, use & 1)) {
-          timed_out = true;
-          break;
-        }
-        const int* svox = reinterpret_cast<const int*>(sp + kStageVoxOff);
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int rr = lane + 32 * k;
-          if (rr < q_rows) {
-            const unsigned char* src = kHalf ? sp + p.out_off + (size_t)rr * out_bytes : rows + (size_t)rr * p.row_stride;
-            bulk_s2g(reinterpret_cast<T*>(p.out) + (int64_t)svox[rr] * C, src, out_bytes);
-          }
-        }
-        bulk_commit();
-        bulk_wait_read_all();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty + s);
-      }
+      if (lane == 0) mbar_arrive(empty + s);
     }
-    if (store_warp) bulk_wait_all();
   }
   if (timed_out) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
   // A timed-out role leaves; the other roles then time out on their own bounded waits.
@@ -568,8 +551,9 @@ static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, cons
   const int C = heads * head_dim;
   s.row_stride = 3 * C * 4 + 16;  // +16 B skews rows across shared-memory banks
   const int rows_bytes = kStageRowsOff + tile * s.row_stride;
-  s.out_off = elt == 2 ? rows_bytes : 0;
-  s.stage_bytes = rows_bytes + (elt == 2 ? tile * C * 2 : 0);
+  s.out_off = 0;
+  s.stage_bytes = rows_bytes;
+  (void)elt;
   const int tf = table_entries(rpb_window, heads);
   s.table_floats = tf * 4 <= kTableSmemMax ? tf : 0;
   const size_t fixed = kBarBytes + ((s.table_floats * 4 + 15) & ~15);

@@ -1,21 +1,22 @@
 // Fused window attention for 16-bit inputs (bf16 / fp16) on tensor cores.
 //
 // Same persistent producer/consumer pipeline as the CUDA-core kernel (one CTA per SM, one producer
-// warp that gathers whole q|k|v rows with one 1-D bulk (TMA) copy per voxel, `full`/`empty`/`done`
-// mbarriers, bulk (TMA) stores of finished rows), but the rows stay 16-bit in shared memory and the
+// warp that gathers whole q|k|v rows with one 1-D bulk (TMA) copy per voxel, `full`/`empty`
+// mbarriers), but the rows stay 16-bit in shared memory and the
 // arithmetic is warp-level MMA (m16n8k16, fp32 accumulation):
 //
 //   * The plan is *padded*: inside a pack every window gets a run of row slots rounded up to
 //     1, 2, 4, 8, 16, 32, 48 or 64, so a 16-slot MMA tile holds whole windows (several when c < 16)
 //     or a 16-row slice of one window.  Unused slots keep stale (finite) data; their keys are
 //     masked out, their query rows are never stored.
-//   * A warp takes (16-slot tile, head) units.  Q comes in as A fragments (ldmatrix), K as B
+//   * A warp takes (16-slot tile, up to three heads) units and interleaves the heads.  Q comes in as A fragments (ldmatrix), K as B
 //     fragments (ldmatrix), S = Q K^T lands in fp32 accumulators whose layout is also the A layout
 //     of the next MMA, so P = softmax(S) is packed to 16 bit in registers and multiplied with V
 //     (ldmatrix.trans).  Windows longer than 16 loop over 16-key blocks with an online softmax.
 //   * Softmax keeps upstream's semantics: the running maximum starts at 0, the denominator gets
 //     +1e-8; bias from the shared-memory table (pre-multiplied by log2 e), -100 shift mask.
-//   * The output tile overwrites the q slice it came from and leaves through bulk stores.
+//   * The output tile overwrites the q slice it came from; the warp then copies it out with
+//     coalesced 16-byte stores.
 //
 // Windows with more voxels than a pack holds are left to the CUDA-core kernel's second phase.
 #include <math.h>
@@ -52,14 +53,13 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
   }
 }
 
-template <typename T, int HD, bool kTableSmem>
-__global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32, 1) k_attn_mma(AttnParams p) {
+template <typename T, int HD, int HU, bool kTableSmem>
+__global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroups) + 32, 1) k_attn_mma(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int tile = p.tile, C = p.C, H = p.H;
   const int S = p.stages, G = p.groups;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + kMaxStages;
-  uint64_t* done = empty + kMaxStages;
   float* table_s = reinterpret_cast<float*>(smem + 256);
   unsigned char* stage0 = smem + 256 + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
   const float* table_base = kTableSmem ? table_s : p.table;
@@ -73,8 +73,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32, 1) k_at
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full + s, 1);
-      mbar_init(empty + s, 1);
-      mbar_init(done + s, kMmaGroupWarps);
+      mbar_init(empty + s, kMmaGroupWarps);  // every warp of the consuming group hands the stage back
     }
     mbar_fence_init();
   }
@@ -83,19 +82,22 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32, 1) k_at
     reinterpret_cast<uint4*>(stage0)[i] = make_uint4(0, 0, 0, 0);
   fence_async_smem();  // order the zero fill before the bulk copies that will land in the same rows
   grid_dependency_wait();
-  if constexpr (kTableSmem)
-    for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) table_s[i] = __ldg(p.table + i) * kLog2e;
+  if constexpr (kTableSmem) stage_table(table_s, p.table, p.table_floats);
   const int n_small = p.header[SSW_H_PACKS_SMALL];
   __syncthreads();
 
   const int my_items = n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   bool timed_out = false;
   if (is_producer) {
-    // slot -> row of the pack: window wl = slot / cpad, i = slot % cpad, valid if wl < nwin && i < c
-    int4 d_cur = make_int4(0, 0, 0, 0), d_nxt = make_int4(0, 0, 0, 0);
-    int vox[2] = {-1, -1}, km[2] = {0, 0};
+    // slot -> row of the pack: window wl = slot / cpad, i = slot % cpad, valid if wl < nwin && i < c.
+    // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
+    // of item i+3 (whose descriptor arrived an iteration ago) are requested while item i is issued,
+    // so no iteration waits on a global load.
+    constexpr int kAhead = 3;
+    int4 dq[kAhead + 2];
+    int vox[kAhead][2], km[kAhead][2];
     auto fetch = [&](const int4& d, int (&v)[2], int (&m)[2]) {
-      const int c = d.y, cpad = slots_of_window(c, 1);
+      const int c = d.y, cpad = slots_of_window(c > 0 ? c : 1, 1);
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int slot = lane + 32 * k;
@@ -108,31 +110,36 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32, 1) k_at
         }
       }
     };
-    if (my_items > 0) d_cur = __ldg(p.pack_desc + blockIdx.x);
-    if (my_items > 1) d_nxt = __ldg(p.pack_desc + blockIdx.x + gridDim.x);
-    if (my_items > 0) fetch(d_cur, vox, km);
+#pragma unroll
+    for (int a = 0; a <= kAhead + 1; ++a)
+      dq[a] = a < my_items ? __ldg(p.pack_desc + blockIdx.x + (size_t)a * gridDim.x) : make_int4(0, 0, 0, 0);
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) fetch(dq[a], vox[a], km[a]);
     for (int i = 0; i < my_items; ++i) {
       const int s = i % S;
       const int use = i / S;
-      int4 d_nn = make_int4(0, 0, 0, 0);
-      if (i + 2 < my_items) d_nn = __ldg(p.pack_desc + blockIdx.x + (size_t)(i + 2) * gridDim.x);
-      int vox_n[2] = {-1, -1}, km_n[2] = {0, 0};
-      if (i + 1 < my_items) fetch(d_nxt, vox_n, km_n);
+      const int4 d_new = i + kAhead + 2 < my_items
+                             ? __ldg(p.pack_desc + blockIdx.x + (size_t)(i + kAhead + 2) * gridDim.x)
+                             : make_int4(0, 0, 0, 0);
+      int vox_n[2], km_n[2];
+      fetch(dq[kAhead], vox_n, km_n);  // item i + kAhead (an all-zero descriptor fetches nothing)
       if (use > 0 && !mbar_wait_bounded(empty + s, (use - 1) & 1)) {
         timed_out = true;
         break;
       }
       unsigned char* st = stage0 + (size_t)s * p.stage_bytes;
+      const int4 d_cur = dq[0];
       if (lane == 0) *reinterpret_cast<int4*>(st) = d_cur;
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int slot = lane + 32 * k;
         if (slot < tile) {
-          reinterpret_cast<int*>(st + kMmaStageVoxOff)[slot] = vox[k];
+          reinterpret_cast<int*>(st + kMmaStageVoxOff)[slot] = vox[0][k];
           // unused slots get neutral metadata so that their (discarded) scores index inside the table
           *reinterpret_cast<int2*>(st + kMmaStageRowsOff + (size_t)slot * p.row_stride + data_bytes) =
-              vox[k] >= 0 ? make_int2(meta_rel(km[k]) * H * 4, meta_region(km[k]) | ((meta_rel(km[k]) + p.rel_off) << 8))
-                          : make_int2(0, p.rel_off << 8);
+              vox[0][k] >= 0
+                  ? make_int2(meta_rel(km[0][k]) * H * 4, meta_region(km[0][k]) | ((meta_rel(km[0][k]) + p.rel_off) << 8))
+                  : make_int2(0, p.rel_off << 8);
         }
       }
       __syncwarp();
@@ -141,22 +148,30 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32, 1) k_at
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
         const int slot = lane + 32 * k;
-        if (slot < tile && vox[k] >= 0)
+        if (slot < tile && vox[0][k] >= 0)
           bulk_g2s(st + kMmaStageRowsOff + (size_t)slot * p.row_stride,
-                   reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[k] * 3 * C, data_bytes, full + s);
+                   reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[0][k] * 3 * C, data_bytes, full + s);
       }
-      d_cur = d_nxt;
-      d_nxt = d_nn;
+#pragma unroll
+      for (int a = 0; a <= kAhead; ++a) dq[a] = dq[a + 1];
+      dq[kAhead + 1] = d_new;
+#pragma unroll
+      for (int a = 0; a + 1 < kAhead; ++a) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          vox[a][k] = vox[a + 1][k];
+          km[a][k] = km[a + 1][k];
+        }
+      }
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        vox[k] = vox_n[k];
-        km[k] = km_n[k];
+        vox[kAhead - 1][k] = vox_n[k];
+        km[kAhead - 1][k] = km_n[k];
       }
     }
   } else {
     const int g = threadIdx.x / gsize;
     const int wg = (threadIdx.x - g * gsize) >> 5;  // warp inside the group
-    const bool store_warp = wg == 0;
     const int qr = lane >> 2, qt = lane & 3;        // fragment coordinates of this lane
     for (int i = g; i < my_items && !timed_out; i += G) {
       const int s = i % S;
@@ -172,51 +187,58 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32, 1) k_at
       const int cpad = slots_of_window(c, 1);
       const int n_mt = (nwin * cpad + 15) >> 4;
       const int nkb = cpad > 16 ? cpad >> 4 : 1;  // 16-key blocks per window
-      for (int u = wg; u < n_mt * H; u += kMmaGroupWarps) {
-        const int mt = u / H, h = u - mt * H;
+      // A unit is (16-slot tile, HU consecutive heads); the HU heads are independent instruction
+      // streams that the unrolled code interleaves, which hides the ldmatrix / MMA / exp latencies.
+      const int n_hg = H / HU;
+      for (int u = wg; u < n_mt * n_hg; u += kMmaGroupWarps) {
+        const int mt = u / n_hg, h0 = (u - mt * n_hg) * HU;
         const int slot_lo = mt * 16 + qr, slot_hi = slot_lo + 8;
         // first key slot of the window(s) this tile belongs to
         const int kbase = cpad > 16 ? (mt * 16 / cpad) * cpad : mt * 16;
         const int2 me_lo = *reinterpret_cast<const int2*>(rows + (size_t)slot_lo * p.row_stride + data_bytes);
         const int2 me_hi = *reinterpret_cast<const int2*>(rows + (size_t)slot_hi * p.row_stride + data_bytes);
-        const unsigned char* tab_lo = reinterpret_cast<const unsigned char*>(table_base + (me_lo.y >> 8) * H + h);
-        const unsigned char* tab_hi = reinterpret_cast<const unsigned char*>(table_base + (me_hi.y >> 8) * H + h);
+        const unsigned char* tab_lo = reinterpret_cast<const unsigned char*>(table_base + (me_lo.y >> 8) * H + h0);
+        const unsigned char* tab_hi = reinterpret_cast<const unsigned char*>(table_base + (me_hi.y >> 8) * H + h0);
         const int reg_lo = me_lo.y & 31, reg_hi = me_hi.y & 31;
         const int win_lo = slot_lo / cpad, win_hi = slot_hi / cpad;  // window of my two query rows
+        const int mi = lane >> 3;
 
-        // Q fragments: HD/16 k-steps
-        uint32_t qf[HD / 16][4];
-        {
-          const int mi = lane >> 3;
+        uint32_t qf[HU][HD / 16][4];
+        float o[HU][HD / 8][4];
+        float m_lo[HU], m_hi[HU], l_lo[HU], l_hi[HU];
+#pragma unroll
+        for (int x = 0; x < HU; ++x) {
           const unsigned char* qp = rows + (size_t)(mt * 16 + (mi & 1) * 8 + (lane & 7)) * p.row_stride +
-                                    (h * HD + (mi >> 1) * 8) * sizeof(T);
+                                    ((h0 + x) * HD + (mi >> 1) * 8) * sizeof(T);
 #pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qf[ks], qp + ks * 16 * sizeof(T));
+          for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qf[x][ks], qp + ks * 16 * sizeof(T));
+#pragma unroll
+          for (int n = 0; n < HD / 8; ++n) o[x][n][0] = o[x][n][1] = o[x][n][2] = o[x][n][3] = 0.f;
+          m_lo[x] = m_hi[x] = 0.f;  // maximum starts from 0 (ops.cu:137)
+          l_lo[x] = l_hi[x] = 0.f;
         }
-        float o[HD / 8][4];
-#pragma unroll
-        for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-        float m_lo = 0.f, m_hi = 0.f, l_lo = 0.f, l_hi = 0.f;  // maximum starts from 0 (ops.cu:137)
 
         for (int kb = 0; kb < nkb; ++kb) {
           const int ks0 = kbase + kb * 16;  // first key slot of this block
-          float sacc[2][4];
+          float sacc[HU][2][4];
 #pragma unroll
-          for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
-          {
-            const int mi = lane >> 3;
+          for (int x = 0; x < HU; ++x) {
+#pragma unroll
+            for (int n = 0; n < 2; ++n) sacc[x][n][0] = sacc[x][n][1] = sacc[x][n][2] = sacc[x][n][3] = 0.f;
             const unsigned char* kp = rows + (size_t)(ks0 + (mi >> 1) * 8 + (lane & 7)) * p.row_stride +
-                                      (C + h * HD + (mi & 1) * 8) * sizeof(T);
+                                      (C + (h0 + x) * HD + (mi & 1) * 8) * sizeof(T);
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
               uint32_t kf[4];
               ldmatrix_x4(kf, kp + ks * 16 * sizeof(T));
-              mma16816<T>(sacc[0], qf[ks], kf[0], kf[1]);
-              mma16816<T>(sacc[1], qf[ks], kf[2], kf[3]);
+              mma16816<T>(sacc[x][0], qf[x][ks], kf[0], kf[1]);
+              mma16816<T>(sacc[x][1], qf[x][ks], kf[2], kf[3]);
             }
           }
-          // scores -> log2 domain, bias, masks
-          float mx_lo = -INFINITY, mx_hi = -INFINITY;
+          // scores -> log2 domain, bias, masks (key metadata is shared by the HU heads)
+          float mx_lo[HU], mx_hi[HU];
+#pragma unroll
+          for (int x = 0; x < HU; ++x) mx_lo[x] = mx_hi[x] = -INFINITY;
 #pragma unroll
           for (int n = 0; n < 2; ++n) {
 #pragma unroll
@@ -225,111 +247,114 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32, 1) k_at
               const int2 km = *reinterpret_cast<const int2*>(rows + (size_t)ks * p.row_stride + data_bytes);
               const int kwin = ks / cpad;
               const bool kvalid = (ks - kwin * cpad) < c && kwin < nwin;
-              const float b_lo = kTableSmem ? *reinterpret_cast<const float*>(tab_lo - km.x)
-                                            : __ldg(reinterpret_cast<const float*>(tab_lo - km.x)) * kLog2e;
-              const float b_hi = kTableSmem ? *reinterpret_cast<const float*>(tab_hi - km.x)
-                                            : __ldg(reinterpret_cast<const float*>(tab_hi - km.x)) * kLog2e;
-              float s_lo = fmaf(sacc[n][e], qscale, b_lo), s_hi = fmaf(sacc[n][2 + e], qscale, b_hi);
-              if (p.use_mask) {
-                const int kr = km.y & 31;
-                if (reg_lo != kr) s_lo += -100.0f * kLog2e;
-                if (reg_hi != kr) s_hi += -100.0f * kLog2e;
+              const bool ok_lo = kvalid && kwin == win_lo, ok_hi = kvalid && kwin == win_hi;
+              const int kr = km.y & 31;
+              const float madd_lo = (p.use_mask && reg_lo != kr) ? -100.0f * kLog2e : 0.f;
+              const float madd_hi = (p.use_mask && reg_hi != kr) ? -100.0f * kLog2e : 0.f;
+#pragma unroll
+              for (int x = 0; x < HU; ++x) {
+                const float b_lo = kTableSmem ? *reinterpret_cast<const float*>(tab_lo - km.x + x * 4)
+                                              : __ldg(reinterpret_cast<const float*>(tab_lo - km.x + x * 4)) * kLog2e;
+                const float b_hi = kTableSmem ? *reinterpret_cast<const float*>(tab_hi - km.x + x * 4)
+                                              : __ldg(reinterpret_cast<const float*>(tab_hi - km.x + x * 4)) * kLog2e;
+                float s_lo = fmaf(sacc[x][n][e], qscale, b_lo) + madd_lo;
+                float s_hi = fmaf(sacc[x][n][2 + e], qscale, b_hi) + madd_hi;
+                s_lo = ok_lo ? s_lo : -INFINITY;
+                s_hi = ok_hi ? s_hi : -INFINITY;
+                sacc[x][n][e] = s_lo;
+                sacc[x][n][2 + e] = s_hi;
+                mx_lo[x] = fmaxf(mx_lo[x], s_lo);
+                mx_hi[x] = fmaxf(mx_hi[x], s_hi);
               }
-              s_lo = (kvalid && kwin == win_lo) ? s_lo : -INFINITY;
-              s_hi = (kvalid && kwin == win_hi) ? s_hi : -INFINITY;
-              sacc[n][e] = s_lo;
-              sacc[n][2 + e] = s_hi;
-              mx_lo = fmaxf(mx_lo, s_lo);
-              mx_hi = fmaxf(mx_hi, s_hi);
             }
           }
-          mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-          mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-          mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-          mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-          if (mx_lo > m_lo) {
-            const float corr = fast_exp2(m_lo - mx_lo);
-            l_lo *= corr;
+          uint32_t pf[HU][4];
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
-            m_lo = mx_lo;
-          }
-          if (mx_hi > m_hi) {
-            const float corr = fast_exp2(m_hi - mx_hi);
-            l_hi *= corr;
+          for (int x = 0; x < HU; ++x) {
+            mx_lo[x] = fmaxf(mx_lo[x], __shfl_xor_sync(0xffffffffu, mx_lo[x], 1));
+            mx_lo[x] = fmaxf(mx_lo[x], __shfl_xor_sync(0xffffffffu, mx_lo[x], 2));
+            mx_hi[x] = fmaxf(mx_hi[x], __shfl_xor_sync(0xffffffffu, mx_hi[x], 1));
+            mx_hi[x] = fmaxf(mx_hi[x], __shfl_xor_sync(0xffffffffu, mx_hi[x], 2));
+            if (mx_lo[x] > m_lo[x]) {
+              const float corr = fast_exp2(m_lo[x] - mx_lo[x]);
+              l_lo[x] *= corr;
 #pragma unroll
-            for (int n = 0; n < HD / 8; ++n) { o[n][2] *= corr; o[n][3] *= corr; }
-            m_hi = mx_hi;
+              for (int n = 0; n < HD / 8; ++n) { o[x][n][0] *= corr; o[x][n][1] *= corr; }
+              m_lo[x] = mx_lo[x];
+            }
+            if (mx_hi[x] > m_hi[x]) {
+              const float corr = fast_exp2(m_hi[x] - mx_hi[x]);
+              l_hi[x] *= corr;
+#pragma unroll
+              for (int n = 0; n < HD / 8; ++n) { o[x][n][2] *= corr; o[x][n][3] *= corr; }
+              m_hi[x] = mx_hi[x];
+            }
+            // P in the A-fragment layout of the next MMA
+            const float p00 = fast_exp2(sacc[x][0][0] - m_lo[x]), p01 = fast_exp2(sacc[x][0][1] - m_lo[x]);
+            const float p02 = fast_exp2(sacc[x][0][2] - m_hi[x]), p03 = fast_exp2(sacc[x][0][3] - m_hi[x]);
+            const float p10 = fast_exp2(sacc[x][1][0] - m_lo[x]), p11 = fast_exp2(sacc[x][1][1] - m_lo[x]);
+            const float p12 = fast_exp2(sacc[x][1][2] - m_hi[x]), p13 = fast_exp2(sacc[x][1][3] - m_hi[x]);
+            l_lo[x] += (p00 + p01) + (p10 + p11);
+            l_hi[x] += (p02 + p03) + (p12 + p13);
+            pf[x][0] = pack2<T>(p00, p01);
+            pf[x][1] = pack2<T>(p02, p03);
+            pf[x][2] = pack2<T>(p10, p11);
+            pf[x][3] = pack2<T>(p12, p13);
           }
-          // P in the A-fragment layout of the next MMA
-          uint32_t pf[4];
-          {
-            const float p00 = fast_exp2(sacc[0][0] - m_lo), p01 = fast_exp2(sacc[0][1] - m_lo);
-            const float p02 = fast_exp2(sacc[0][2] - m_hi), p03 = fast_exp2(sacc[0][3] - m_hi);
-            const float p10 = fast_exp2(sacc[1][0] - m_lo), p11 = fast_exp2(sacc[1][1] - m_lo);
-            const float p12 = fast_exp2(sacc[1][2] - m_hi), p13 = fast_exp2(sacc[1][3] - m_hi);
-            l_lo += (p00 + p01) + (p10 + p11);
-            l_hi += (p02 + p03) + (p12 + p13);
-            pf[0] = pack2<T>(p00, p01);
-            pf[1] = pack2<T>(p02, p03);
-            pf[2] = pack2<T>(p10, p11);
-            pf[3] = pack2<T>(p12, p13);
-          }
-          {
-            const int mi = lane >> 3;
+#pragma unroll
+          for (int x = 0; x < HU; ++x) {
             const unsigned char* vp = rows + (size_t)(ks0 + (mi & 1) * 8 + (lane & 7)) * p.row_stride +
-                                      (2 * C + h * HD + (mi >> 1) * 8) * sizeof(T);
+                                      (2 * C + (h0 + x) * HD + (mi >> 1) * 8) * sizeof(T);
 #pragma unroll
             for (int n = 0; n < HD / 8; n += 2) {
               uint32_t vf[4];
               ldmatrix_x4_trans(vf, vp + n * 8 * sizeof(T));
-              mma16816<T>(o[n], pf, vf[0], vf[1]);
-              mma16816<T>(o[n + 1], pf, vf[2], vf[3]);
+              mma16816<T>(o[x][n], pf[x], vf[0], vf[1]);
+              mma16816<T>(o[x][n + 1], pf[x], vf[2], vf[3]);
             }
           }
         }
-        // row sums live in four lanes each
-        l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-        l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-        const float inv_lo = 1.0f / (l_lo + 1e-8f), inv_hi = 1.0f / (l_hi + 1e-8f);  // ops.cu:164
-        // the q slice this tile was read from becomes its output slice
         __syncwarp();
-        uint32_t* out_lo = reinterpret_cast<uint32_t*>(rows + (size_t)slot_lo * p.row_stride + (h * HD) * sizeof(T)) + qt;
-        uint32_t* out_hi = reinterpret_cast<uint32_t*>(rows + (size_t)slot_hi * p.row_stride + (h * HD) * sizeof(T)) + qt;
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) {
-          out_lo[n * 4] = pack2<T>(o[n][0] * inv_lo, o[n][1] * inv_lo);
-          out_hi[n * 4] = pack2<T>(o[n][2] * inv_hi, o[n][3] * inv_hi);
-        }
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(done + s);
-      if (store_warp) {
-        if (!mbar_wait_bounded(done + s, use & 1)) {
-          timed_out = true;
-          break;
-        }
-        const int* svox = reinterpret_cast<const int*>(sp + kMmaStageVoxOff);
+        for (int x = 0; x < HU; ++x) {
+          // row sums live in four lanes each
+          float ll = l_lo[x], lh = l_hi[x];
+          ll += __shfl_xor_sync(0xffffffffu, ll, 1);
+          ll += __shfl_xor_sync(0xffffffffu, ll, 2);
+          lh += __shfl_xor_sync(0xffffffffu, lh, 1);
+          lh += __shfl_xor_sync(0xffffffffu, lh, 2);
+          const float inv_lo = 1.0f / (ll + 1e-8f), inv_hi = 1.0f / (lh + 1e-8f);  // ops.cu:164
+          // the q slice this tile was read from becomes its output slice
+          uint32_t* out_lo =
+              reinterpret_cast<uint32_t*>(rows + (size_t)slot_lo * p.row_stride + ((h0 + x) * HD) * sizeof(T)) + qt;
+          uint32_t* out_hi =
+              reinterpret_cast<uint32_t*>(rows + (size_t)slot_hi * p.row_stride + ((h0 + x) * HD) * sizeof(T)) + qt;
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int slot = lane + 32 * k;
-          if (slot < tile) {
-            const int v = svox[slot];
-            if (v >= 0)
-              bulk_s2g(reinterpret_cast<T*>(p.out) + (int64_t)v * C, rows + (size_t)slot * p.row_stride,
-                       C * sizeof(T));
+          for (int n = 0; n < HD / 8; ++n) {
+            out_lo[n * 4] = pack2<T>(o[x][n][0] * inv_lo, o[x][n][1] * inv_lo);
+            out_hi[n * 4] = pack2<T>(o[x][n][2] * inv_hi, o[x][n][3] * inv_hi);
           }
         }
-        bulk_commit();
-        bulk_wait_read_all();
+        // The tile's 16 x (HU*HD) outputs now sit in shared memory in row order: copy them out with
+        // 16-byte stores, a run of HU*HD elements per voxel row (bulk stores of whole rows were
+        // tried; one bulk operation per row is what bounds them).
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty + s);
+        {
+          constexpr int kChunks = HU * HD / 8;  // 16-byte chunks per row segment
+          const int* svox = reinterpret_cast<const int*>(sp + kMmaStageVoxOff);
+          for (int idx = lane; idx < 16 * kChunks; idx += 32) {
+            const int rr = idx / kChunks, cc = idx - rr * kChunks;
+            const int slot = mt * 16 + rr;
+            const int v = svox[slot];
+            if (v >= 0)
+              *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + (int64_t)v * C + h0 * HD + cc * 8) =
+                  *reinterpret_cast<const uint4*>(rows + (size_t)slot * p.row_stride + (h0 * HD + cc * 8) * sizeof(T));
+          }
+        }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty + s);
     }
-    if (store_warp) bulk_wait_all();
   }
   if (timed_out) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
   __syncthreads();
@@ -375,22 +400,30 @@ int mma_default_tile(int heads, int head_dim, const int32_t rpb_window[3]) {
   return 16;
 }
 
-template <typename T, int HD>
+template <typename T, int HD, int HU>
 static int launch_mma(AttnParams p, const MmaShape& s, cudaStream_t stream) {
   int dev = 0, sms = 0;
   SSW_CUDA_TRY(cudaGetDevice(&dev));
   SSW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const int threads = s.groups * kMmaGroupWarps * 32 + 32;
+  if (HU == 3 && p.groups > 3) p.groups = 3;  // three interleaved heads need the larger register budget
+  const int threads = p.groups * kMmaGroupWarps * 32 + 32;
   if (s.table_floats > 0) {
-    auto kern = k_attn_mma<T, HD, true>;
+    auto kern = k_attn_mma<T, HD, HU, true>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem));
     SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), s.smem, stream, p));
   } else {
-    auto kern = k_attn_mma<T, HD, false>;
+    auto kern = k_attn_mma<T, HD, HU, false>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem));
     SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), s.smem, stream, p));
   }
   return SSW_OK;
+}
+
+template <typename T, int HD>
+static int launch_mma_heads(const AttnParams& p, const MmaShape& s, cudaStream_t stream) {
+  if (p.H % 3 == 0) return launch_mma<T, HD, 3>(p, s, stream);
+  if (p.H % 2 == 0) return launch_mma<T, HD, 2>(p, s, stream);
+  return launch_mma<T, HD, 1>(p, s, stream);
 }
 
 // Packs of a padded plan, 16-bit inputs.  `p` arrives with the plan pointers, qkv/out/table, H, C,
@@ -404,11 +437,11 @@ int run_attn_mma(AttnParams p, int dtype, int head_dim, const int32_t rpb_window
   p.stage_bytes = s.stage_bytes;
   p.table_floats = s.table_floats;
   if (dtype == SSW_BF16) {
-    if (head_dim == 16) return launch_mma<__nv_bfloat16, 16>(p, s, stream);
-    if (head_dim == 32) return launch_mma<__nv_bfloat16, 32>(p, s, stream);
+    if (head_dim == 16) return launch_mma_heads<__nv_bfloat16, 16>(p, s, stream);
+    if (head_dim == 32) return launch_mma_heads<__nv_bfloat16, 32>(p, s, stream);
   } else if (dtype == SSW_F16) {
-    if (head_dim == 16) return launch_mma<__half, 16>(p, s, stream);
-    if (head_dim == 32) return launch_mma<__half, 32>(p, s, stream);
+    if (head_dim == 16) return launch_mma_heads<__half, 16>(p, s, stream);
+    if (head_dim == 32) return launch_mma_heads<__half, 32>(p, s, stream);
   }
   return SSW_E_UNSUPPORTED;
 }
