@@ -94,6 +94,9 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
     // of item i+3 (whose descriptor arrived an iteration ago) are requested while item i is issued,
     // so no iteration waits on a global load.
     constexpr int kAhead = 3;
+    // The plan lists packs by ascending occupancy; walking the list backwards puts the long items
+    // first and leaves the short ones for the tail of the kernel.
+    auto item_index = [&](int k) { return n_small - 1 - ((int)blockIdx.x + k * (int)gridDim.x); };
     int4 dq[kAhead + 2];
     int vox[kAhead][2], km[kAhead][2];
     auto fetch = [&](const int4& d, int (&v)[2], int (&m)[2]) {
@@ -112,14 +115,14 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
     };
 #pragma unroll
     for (int a = 0; a <= kAhead + 1; ++a)
-      dq[a] = a < my_items ? __ldg(p.pack_desc + blockIdx.x + (size_t)a * gridDim.x) : make_int4(0, 0, 0, 0);
+      dq[a] = a < my_items ? __ldg(p.pack_desc + item_index(a)) : make_int4(0, 0, 0, 0);
 #pragma unroll
     for (int a = 0; a < kAhead; ++a) fetch(dq[a], vox[a], km[a]);
     for (int i = 0; i < my_items; ++i) {
       const int s = i % S;
       const int use = i / S;
       const int4 d_new = i + kAhead + 2 < my_items
-                             ? __ldg(p.pack_desc + blockIdx.x + (size_t)(i + kAhead + 2) * gridDim.x)
+                             ? __ldg(p.pack_desc + item_index(i + kAhead + 2))
                              : make_int4(0, 0, 0, 0);
       int vox_n[2], km_n[2];
       fetch(dq[kAhead], vox_n, km_n);  // item i + kAhead (an all-zero descriptor fetches nothing)
