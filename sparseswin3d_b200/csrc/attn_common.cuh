@@ -12,7 +12,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 constexpr int kMaxStages = 6;
 constexpr int kMaxGroups = 4;
-constexpr int kMaxTile = 64;
+constexpr int kMaxTile = 64, kMaxProducerWarps = 4;
 
 struct AttnParams {
   const void* qkv;
@@ -29,6 +29,7 @@ struct AttnParams {
   int H, C, tile, HG;
   int group_threads;  // threads of one consumer group (multiple of 32) = ceil32(tile * HG)
   int groups, stages;
+  int prod_warps;     // warps that issue the row copies of an item
   float scale;
   int use_mask;
   int row_stride;     // bytes between fp32 rows in a stage

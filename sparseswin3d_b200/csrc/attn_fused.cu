@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full + s, 1);
+      mbar_init(full + s, p.prod_warps);  // one arrive (with its byte count) per producer warp
       mbar_init(empty + s, gwarps);  // every warp of the consuming group hands the stage back
     }
     for (int g = 0; g < G; ++g) mbar_init(gbar + g, gwarps);
@@ -309,7 +309,10 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
     // of item i+3 (whose descriptor arrived an iteration ago) are requested while item i is issued,
     // so no iteration waits on a global load.
+    // The rows of an item are dealt round-robin to the producer warps: a warp submits its bulk
+    // copies one lane after the other, so several warps submit several rows at a time.
     constexpr int kAhead = 3;
+    const int PW = p.prod_warps, pw = ((int)threadIdx.x - n_cons) >> 5;
     // The plan lists packs by ascending occupancy; walking the list backwards puts the long items
     // first and leaves the short ones for the tail of the kernel.
     auto item_index = [&](int k) { return n_small - 1 - ((int)blockIdx.x + k * (int)gridDim.x); };
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       const int nr = d.z * d.y;
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int rr = lane + 32 * k;
+        const int rr = (lane + 32 * k) * PW + pw;
         v[k] = 0;
         m[k] = 0;
         if (rr < nr) {
@@ -348,22 +351,23 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       unsigned char* st = stage0 + (size_t)s * p.stage_bytes;
       const int4 d_cur = dq[0];
       const int nr = d_cur.z * d_cur.y;
-      if (lane == 0) *reinterpret_cast<int4*>(st) = d_cur;
+      if (lane == 0 && pw == 0) *reinterpret_cast<int4*>(st) = d_cur;
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int rr = lane + 32 * k;
+        const int rr = (lane + 32 * k) * PW + pw;
         if (rr < nr) {
           reinterpret_cast<int*>(st + kStageVoxOff)[rr] = vox[0][k];
           *reinterpret_cast<int2*>(st + kStageRowsOff + (size_t)rr * p.row_stride + data_bytes) = make_int2(
               meta_rel(km[0][k]) * H * 4, meta_region(km[0][k]) | ((meta_rel(km[0][k]) + p.rel_off) << 8));
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_expect_tx(full + s, nr * copy_bytes);
+      // rows pw, pw + PW, ... below nr are this warp's
+      const int my_rows = nr > pw ? (nr - pw + PW - 1) / PW : 0;
+      if (lane == 0) mbar_expect_tx(full + s, (uint32_t)my_rows * copy_bytes);
       __syncwarp();
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int rr = lane + 32 * k;
+        const int rr = (lane + 32 * k) * PW + pw;
         if (rr < nr)
           bulk_g2s(st + kStageRowsOff + (size_t)rr * p.row_stride + copy_off,
                    reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[0][k] * 3 * C, copy_bytes, full + s);
@@ -537,7 +541,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
 constexpr int kTableSmemMax = 40 * 1024;
 constexpr size_t kSmemBudget = 226 * 1024;
 struct KernelShape {
-  int hg, group_threads, groups, stages, row_stride, stage_bytes, out_off, table_floats;
+  int hg, group_threads, groups, stages, prod_warps, row_stride, stage_bytes, out_off, table_floats;
   size_t smem;
 };
 static int table_entries(const int32_t w[3], int heads) {
@@ -566,7 +570,12 @@ static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, cons
   // one stage is always in flight; at most 1024 threads
   int groups = stages - 1;
   if (groups > kMaxGroups) groups = kMaxGroups;
-  while (groups > 1 && groups * s.group_threads + 32 > 1024) --groups;
+  s.prod_warps = 2;
+  if (const char* e = getenv("SSW_PROD_WARPS")) {  // tuning override (experiments only)
+    const int v = atoi(e);
+    if (v >= 1 && v <= kMaxProducerWarps) s.prod_warps = v;
+  }
+  while (groups > 1 && groups * s.group_threads + 32 * s.prod_warps > 1024) --groups;
   if (groups < 1) groups = 1;
   // Tuning overrides (experiments only): SSW_STAGES / SSW_GROUPS within the shared-memory budget.
   if (const char* e = getenv("SSW_STAGES")) {
@@ -575,7 +584,7 @@ static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, cons
   }
   if (const char* e = getenv("SSW_GROUPS")) {
     const int v = atoi(e);
-    if (v >= 1 && v <= kMaxGroups && v <= stages && v * s.group_threads + 32 <= 1024) groups = v;
+    if (v >= 1 && v <= kMaxGroups && v <= stages && v * s.group_threads + 32 * s.prod_warps <= 1024) groups = v;
   }
   s.groups = groups;
   s.smem = fixed + (size_t)(stages > 0 ? stages : 1) * s.stage_bytes;
@@ -649,7 +658,7 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   if (tile > kMaxTile) return SSW_E_UNSUPPORTED;
   const KernelShape s = kernel_shape(tile, heads, head_dim, elt, rpb_window);
   if (s.stages < 2 || s.smem > 227 * 1024) return SSW_E_UNSUPPORTED;
-  const int threads = s.groups * s.group_threads + 32;
+  const int threads = s.groups * s.group_threads + 32 * s.prod_warps;
   AttnParams p;
   p.qkv = qkv;
   p.out = out;
@@ -670,6 +679,7 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   p.group_threads = s.group_threads;
   p.groups = s.groups;
   p.stages = s.stages;
+  p.prod_warps = s.prod_warps;
   p.scale = scale;
   p.use_mask = use_mask;
   p.row_stride = s.row_stride;

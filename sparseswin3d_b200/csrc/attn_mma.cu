@@ -53,8 +53,14 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
   }
 }
 
+// Layout of a staged row's metadata word .y: region (5 bits), window inside the pack (7 bits: 0..63,
+// kMmaPadWindow for unused slots), row of the bias table (from bit 12).
+constexpr int kMmaRelShift = 12;
+constexpr int kMmaPadWindow = 64;
+constexpr int kMmaWindowBits = 127 << 5;
+
 template <typename T, int HD, int HU, bool kTableSmem>
-__global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroups) + 32, 1) k_attn_mma(AttnParams p) {
+__global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroups) + 32 * kMaxProducerWarps, 1) k_attn_mma(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int tile = p.tile, C = p.C, H = p.H;
   const int S = p.stages, G = p.groups;
@@ -72,7 +78,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full + s, 1);
+      mbar_init(full + s, p.prod_warps);       // one arrive (with its byte count) per producer warp
       mbar_init(empty + s, kMmaGroupWarps);  // every warp of the consuming group hands the stage back
     }
     mbar_fence_init();
@@ -93,7 +99,10 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
     // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
     // of item i+3 (whose descriptor arrived an iteration ago) are requested while item i is issued,
     // so no iteration waits on a global load.
+    // The rows of an item are dealt round-robin to the producer warps: a warp submits its bulk
+    // copies one lane after the other, so several warps submit several rows at a time.
     constexpr int kAhead = 3;
+    const int PW = p.prod_warps, pw = ((int)threadIdx.x - n_cons) >> 5;
     // The plan lists packs by ascending occupancy; walking the list backwards puts the long items
     // first and leaves the short ones for the tail of the kernel.
     auto item_index = [&](int k) { return n_small - 1 - ((int)blockIdx.x + k * (int)gridDim.x); };
@@ -103,13 +112,14 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
       const int c = d.y, cpad = slots_of_window(c > 0 ? c : 1, 1);
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int slot = lane + 32 * k;
+        const int slot = (lane + 32 * k) * PW + pw;
         const int wl = slot / cpad, i = slot - wl * cpad;
         v[k] = -1;
         m[k] = 0;
         if (slot < tile && wl < d.z && i < c) {
           v[k] = __ldg(p.pack_perm + d.x + wl * c + i);
-          m[k] = __ldg(p.pack_meta + d.x + wl * c + i);
+          // the in-window position is not needed here: its bits carry the window's index in the pack
+          m[k] = (__ldg(p.pack_meta + d.x + wl * c + i) & ~1023) | wl;
         }
       }
     };
@@ -132,25 +142,28 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
       }
       unsigned char* st = stage0 + (size_t)s * p.stage_bytes;
       const int4 d_cur = dq[0];
-      if (lane == 0) *reinterpret_cast<int4*>(st) = d_cur;
+      if (lane == 0 && pw == 0) *reinterpret_cast<int4*>(st) = d_cur;
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int slot = lane + 32 * k;
+        const int slot = (lane + 32 * k) * PW + pw;
         if (slot < tile) {
           reinterpret_cast<int*>(st + kMmaStageVoxOff)[slot] = vox[0][k];
-          // unused slots get neutral metadata so that their (discarded) scores index inside the table
+          // Row metadata: .x = byte offset of the row's relative-position code in the bias table,
+          // .y = region | window-in-pack << 5 | table row << 12.  Unused slots form a window of their
+          // own (kMmaPadWindow) with neutral codes, so their (discarded) scores index inside the table.
           *reinterpret_cast<int2*>(st + kMmaStageRowsOff + (size_t)slot * p.row_stride + data_bytes) =
-              vox[0][k] >= 0
-                  ? make_int2(meta_rel(km[0][k]) * H * 4, meta_region(km[0][k]) | ((meta_rel(km[0][k]) + p.rel_off) << 8))
-                  : make_int2(0, p.rel_off << 8);
+              vox[0][k] >= 0 ? make_int2(meta_rel(km[0][k]) * H * 4,
+                                         meta_region(km[0][k]) | ((km[0][k] & 1023) << 5) |
+                                             ((meta_rel(km[0][k]) + p.rel_off) << kMmaRelShift))
+                             : make_int2(0, (kMmaPadWindow << 5) | (p.rel_off << kMmaRelShift));
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_expect_tx(full + s, (uint32_t)(d_cur.z * d_cur.y) * (uint32_t)data_bytes);
+      const int my_rows = __popc(__ballot_sync(0xffffffffu, vox[0][0] >= 0)) + __popc(__ballot_sync(0xffffffffu, vox[0][1] >= 0));
+      if (lane == 0) mbar_expect_tx(full + s, (uint32_t)my_rows * (uint32_t)data_bytes);
       __syncwarp();
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int slot = lane + 32 * k;
+        const int slot = (lane + 32 * k) * PW + pw;
         if (slot < tile && vox[0][k] >= 0)
           bulk_g2s(st + kMmaStageRowsOff + (size_t)slot * p.row_stride,
                    reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[0][k] * 3 * C, data_bytes, full + s);
@@ -200,11 +213,12 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
         const int kbase = cpad > 16 ? (mt * 16 / cpad) * cpad : mt * 16;
         const int2 me_lo = *reinterpret_cast<const int2*>(rows + (size_t)slot_lo * p.row_stride + data_bytes);
         const int2 me_hi = *reinterpret_cast<const int2*>(rows + (size_t)slot_hi * p.row_stride + data_bytes);
-        const unsigned char* tab_lo = reinterpret_cast<const unsigned char*>(table_base + (me_lo.y >> 8) * H + h0);
-        const unsigned char* tab_hi = reinterpret_cast<const unsigned char*>(table_base + (me_hi.y >> 8) * H + h0);
-        const int reg_lo = me_lo.y & 31, reg_hi = me_hi.y & 31;
-        const int win_lo = slot_lo / cpad, win_hi = slot_hi / cpad;  // window of my two query rows
+        const unsigned char* tab_lo =
+            reinterpret_cast<const unsigned char*>(table_base + (me_lo.y >> kMmaRelShift) * H + h0);
+        const unsigned char* tab_hi =
+            reinterpret_cast<const unsigned char*>(table_base + (me_hi.y >> kMmaRelShift) * H + h0);
         const int mi = lane >> 3;
+        const int region_bits = p.use_mask ? 31 : 0;
 
         uint32_t qf[HU][HD / 16][4];
         float o[HU][HD / 8][4];
@@ -248,12 +262,11 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
             for (int e = 0; e < 2; ++e) {
               const int ks = ks0 + n * 8 + qt * 2 + e;  // key slot of this column
               const int2 km = *reinterpret_cast<const int2*>(rows + (size_t)ks * p.row_stride + data_bytes);
-              const int kwin = ks / cpad;
-              const bool kvalid = (ks - kwin * cpad) < c && kwin < nwin;
-              const bool ok_lo = kvalid && kwin == win_lo, ok_hi = kvalid && kwin == win_hi;
-              const int kr = km.y & 31;
-              const float madd_lo = (p.use_mask && reg_lo != kr) ? -100.0f * kLog2e : 0.f;
-              const float madd_hi = (p.use_mask && reg_hi != kr) ? -100.0f * kLog2e : 0.f;
+              // one XOR per (query row, key) tells both: same window (bits 5..11), same region (bits 0..4)
+              const int x_lo = km.y ^ me_lo.y, x_hi = km.y ^ me_hi.y;
+              const bool ok_lo = (x_lo & kMmaWindowBits) == 0, ok_hi = (x_hi & kMmaWindowBits) == 0;
+              const float madd_lo = (x_lo & region_bits) ? -100.0f * kLog2e : 0.f;
+              const float madd_hi = (x_hi & region_bits) ? -100.0f * kLog2e : 0.f;
 #pragma unroll
               for (int x = 0; x < HU; ++x) {
                 const float b_lo = kTableSmem ? *reinterpret_cast<const float*>(tab_lo - km.x + x * 4)
@@ -409,7 +422,12 @@ static int launch_mma(AttnParams p, const MmaShape& s, cudaStream_t stream) {
   SSW_CUDA_TRY(cudaGetDevice(&dev));
   SSW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   if (HU == 3 && p.groups > 3) p.groups = 3;  // three interleaved heads need the larger register budget
-  const int threads = p.groups * kMmaGroupWarps * 32 + 32;
+  p.prod_warps = 4;  // 576-byte rows: the copy submission rate, not the bytes, bounds the producer
+  if (const char* e = getenv("SSW_PROD_WARPS")) {  // tuning override (experiments only)
+    const int v = atoi(e);
+    if (v >= 1 && v <= kMaxProducerWarps) p.prod_warps = v;
+  }
+  const int threads = p.groups * kMmaGroupWarps * 32 + 32 * p.prod_warps;
   if (s.table_floats > 0) {
     auto kern = k_attn_mma<T, HD, HU, true>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem));
@@ -422,10 +440,10 @@ static int launch_mma(AttnParams p, const MmaShape& s, cudaStream_t stream) {
   return SSW_OK;
 }
 
+// One head per consumer unit: interleaving two or three heads in a unit was measured slower (more
+// registers, fewer units to spread over the warps of a group).
 template <typename T, int HD>
 static int launch_mma_heads(const AttnParams& p, const MmaShape& s, cudaStream_t stream) {
-  if (p.H % 3 == 0) return launch_mma<T, HD, 3>(p, s, stream);
-  if (p.H % 2 == 0) return launch_mma<T, HD, 2>(p, s, stream);
   return launch_mma<T, HD, 1>(p, s, stream);
 }
 
