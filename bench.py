@@ -37,10 +37,14 @@ UNIT = "voxels/s"
 N_VOX = 150_000
 HEADS, HEAD_DIM, WINDOW, SHIFT = 3, 32, (7, 7, 7), (3, 3, 3)
 C = HEADS * HEAD_DIM
-KERNELS_PER_PASS = 6  # k_count, k_reduce, k_compact, k_order, k_scatter, k_attn_fused
-# DRAM bytes one k_attn_fused launch moves on this workload (dram__bytes_read.sum + dram__bytes_write.sum
-# of an ncu capture, see profiles/); None until a capture exists for the dtype.
-NCU_TRAFFIC_BYTES = {"f32": None, "bf16": None}
+# kernels of this library per pass: k_count, k_reduce, k_compact, k_order, k_scatter, then k_attn_fused
+# (fp32) or k_attn_mma + the k_attn_fused launch that takes the windows larger than a tile (bf16)
+KERNELS_PER_PASS = {"f32": 6, "bf16": 7}
+DOMINANT_KERNEL = {"f32": "k_attn_fused", "bf16": "k_attn_mma"}
+# DRAM bytes one launch of the dominant kernel moves on this workload (dram__bytes_read.sum +
+# dram__bytes_write.sum of the ncu captures summarised under profiles/).  Part of the output is still
+# in L2 when the kernel ends, which is why the figure is below the algorithmic bytes.
+NCU_TRAFFIC_BYTES = {"f32": 210_873_344, "bf16": 99_223_552}
 
 
 def algorithmic_bytes_per_voxel(elt: int) -> int:
@@ -218,7 +222,7 @@ def run_ours(args):
     ms = float(t.item())
     value = 2.0 * N_VOX * world * args.steps / (ms * 1e-3)
 
-    # ---- dominant kernel alone: graphs of `reps` back-to-back k_attn_fused launches ----------
+    # ---- dominant kernel alone: graphs of `reps` back-to-back attention calls -----------------
     plans = [window.bucket_windows(coords=coords, geom=g, rpb_window=WINDOW, tile_rows=tile, padded=bool(padded)) for g in geoms]
     torch.cuda.synchronize()
     reps = 12
@@ -298,11 +302,11 @@ def run_ours(args):
         "clocks": clk.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": k_e2e},
-        "gpu_launches": KERNELS_PER_PASS * 2 * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "k_attn_fused", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "gpu_launches": KERNELS_PER_PASS[args.dtype] * 2 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": DOMINANT_KERNEL[args.dtype], "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES[args.dtype],
                      "algorithmic_bytes": alg_bytes, "kernel_ms": k_ms, "bucketing_ms": b_ms,
-                     "timing": "CUDA events around a replayed CUDA graph of 12 back-to-back launches, median of 5"},
+                     "timing": "CUDA events around a replayed CUDA graph of 12 back-to-back attention calls, median of 5"},
     }
     if world > 1:
         dist.barrier()
