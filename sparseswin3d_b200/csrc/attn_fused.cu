@@ -295,7 +295,6 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   grid_dependency_wait();
   const int n_small = p.header[SSW_H_PACKS_SMALL];
   const int n_items = p.header[SSW_H_PACKS];
-  if (p.skip_packs && n_items <= n_small) return;  // launched for the large windows only and there are none
   if constexpr (kTableSmem) stage_table(table_s, p.table, p.table_floats);
   __syncthreads();
 
@@ -303,7 +302,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   // Phase A: packs, producer / consumer pipeline
   // ------------------------------------------------------------------------------------------
   const int my_items =
-      (!p.skip_packs && n_small > (int)blockIdx.x) ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   bool timed_out = false;
   if (is_producer) {
     // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
@@ -686,14 +685,11 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   p.stage_bytes = s.stage_bytes;
   p.out_off = s.out_off;
   p.table_floats = s.table_floats;
-  p.skip_packs = 0;
   cudaStream_t stream = (cudaStream_t)stream_;
   if (L->padded) {
-    // padded plan: the packs go to the tensor-core kernel, windows beyond a pack to phase B below
+    // padded plan: the tensor-core kernel takes both the packs and the windows beyond a pack
     if (elt != 2 || attn_vals) return SSW_E_INVALID;
-    const int rc = run_attn_mma(p, dtype, head_dim, rpb_window, stream);
-    if (rc != SSW_OK) return rc;
-    p.skip_packs = 1;
+    return run_attn_mma(p, dtype, head_dim, rpb_window, stream);
   }
   switch (dtype) {
     case SSW_F32: return dispatch<float>(p, head_dim, threads, s.smem, stream);

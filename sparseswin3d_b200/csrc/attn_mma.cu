@@ -1,24 +1,28 @@
 // Fused window attention for 16-bit inputs (bf16 / fp16) on tensor cores.
 //
-// Same persistent producer/consumer pipeline as the CUDA-core kernel (one CTA per SM, one producer
-// warp that gathers whole q|k|v rows with one 1-D bulk (TMA) copy per voxel, `full`/`empty`
-// mbarriers), but the rows stay 16-bit in shared memory and the
-// arithmetic is warp-level MMA (m16n8k16, fp32 accumulation):
+// Same persistent producer/consumer pipeline as the CUDA-core kernel (one CTA per SM, producer
+// warps that gather voxel rows with one 1-D bulk (TMA) copy per row, `full`/`empty` mbarriers with
+// bounded waits), but the rows stay 16-bit in shared memory and the arithmetic is warp-level MMA
+// (m16n8k16, fp32 accumulation):
 //
 //   * The plan is *padded*: inside a pack every window gets a run of row slots rounded up to
 //     1, 2, 4, 8, 16, 32, 48 or 64, so a 16-slot MMA tile holds whole windows (several when c < 16)
-//     or a 16-row slice of one window.  Unused slots keep stale (finite) data; their keys are
-//     masked out, their query rows are never stored.
-//   * A warp takes (16-slot tile, up to three heads) units and interleaves the heads.  Q comes in as A fragments (ldmatrix), K as B
+//     or a 16-row slice of one window.  Unused slots hold zeros or stale (finite) rows; their keys
+//     are masked out, their query rows are never stored.
+//   * A unit of work is (16-slot tile, head).  Q comes in as A fragments (ldmatrix), K as B
 //     fragments (ldmatrix), S = Q K^T lands in fp32 accumulators whose layout is also the A layout
 //     of the next MMA, so P = softmax(S) is packed to 16 bit in registers and multiplied with V
-//     (ldmatrix.trans).  Windows longer than 16 loop over 16-key blocks with an online softmax.
+//     (ldmatrix.trans).  Longer key ranges loop over 16-key blocks with an online softmax.
 //   * Softmax keeps upstream's semantics: the running maximum starts at 0, the denominator gets
 //     +1e-8; bias from the shared-memory table (pre-multiplied by log2 e), -100 shift mask.
 //   * The output tile overwrites the q slice it came from; the warp then copies it out with
 //     coalesced 16-byte stores.
 //
-// Windows with more voxels than a pack holds are left to the CUDA-core kernel's second phase.
+// Phase 1 (packs): every consumer group of four warps takes whole work items, one per pipeline
+// stage.  Phase 2 (windows with more voxels than a pack holds): a work item is one tile of query
+// rows of such a window; its q rows sit in stage 0 while the window's k|v rows stream through the
+// other stages tile by tile, and all consumer warps work on the same key tile, each on its own
+// (16 query rows, head) unit whose accumulators stay in registers for the whole window.
 #include <math.h>
 #include <stdlib.h>
 
@@ -29,6 +33,11 @@ namespace ssw {
 constexpr int kMmaGroupWarps = 4;
 constexpr int kMmaStageVoxOff = 16;
 constexpr int kMmaStageRowsOff = kMmaStageVoxOff + kMaxTile * 4;
+// Layout of a staged row's metadata word .y: region (5 bits), window inside the pack (7 bits: 0..63,
+// kMmaPadWindow for unused slots), row of the bias table (from bit 12).
+constexpr int kMmaRelShift = 12;
+constexpr int kMmaPadWindow = 64;
+constexpr int kMmaWindowBits = 127 << 5;
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -53,34 +62,197 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
   }
 }
 
-// Layout of a staged row's metadata word .y: region (5 bits), window inside the pack (7 bits: 0..63,
-// kMmaPadWindow for unused slots), row of the bias table (from bit 12).
-constexpr int kMmaRelShift = 12;
-constexpr int kMmaPadWindow = 64;
-constexpr int kMmaWindowBits = 127 << 5;
+// Metadata of a staged row (see kMmaRelShift): what the producer writes behind the row's data.
+__device__ __forceinline__ int2 row_meta(int m, int window, int H, int rel_off) {
+  return make_int2(meta_rel(m) * H * 4, meta_region(m) | (window << 5) | ((meta_rel(m) + rel_off) << kMmaRelShift));
+}
+__device__ __forceinline__ int2 pad_meta(int rel_off) {
+  return make_int2(0, (kMmaPadWindow << 5) | (rel_off << kMmaRelShift));
+}
 
-template <typename T, int HD, int HU, bool kTableSmem>
-__global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroups) + 32 * kMaxProducerWarps, 1) k_attn_mma(AttnParams p) {
+// One (16 query rows, head) unit: the q fragments, the two rows' metadata, the running softmax and
+// the output accumulators of this lane (rows lane/4 and lane/4 + 8 of the tile).
+template <int HD>
+struct MmaUnit {
+  uint32_t qf[HD / 16][4];
+  float o[HD / 8][4];
+  float m_lo, m_hi, l_lo, l_hi;
+  int me_lo_y, me_hi_y;
+  const unsigned char* tab_lo;
+  const unsigned char* tab_hi;
+};
+
+// Start a unit on query slots [slot0, slot0 + 16) of the staged rows, head h.
+template <typename T, int HD>
+__device__ __forceinline__ void unit_begin(MmaUnit<HD>& u, const unsigned char* rows, int row_stride, int data_bytes,
+                                           int slot0, int h, int H, const float* table_base, int lane) {
+  const int qr = lane >> 2, mi = lane >> 3;
+  const int2 me_lo = *reinterpret_cast<const int2*>(rows + (size_t)(slot0 + qr) * row_stride + data_bytes);
+  const int2 me_hi = *reinterpret_cast<const int2*>(rows + (size_t)(slot0 + qr + 8) * row_stride + data_bytes);
+  u.me_lo_y = me_lo.y;
+  u.me_hi_y = me_hi.y;
+  u.tab_lo = reinterpret_cast<const unsigned char*>(table_base + (me_lo.y >> kMmaRelShift) * H + h);
+  u.tab_hi = reinterpret_cast<const unsigned char*>(table_base + (me_hi.y >> kMmaRelShift) * H + h);
+  const unsigned char* qp =
+      rows + (size_t)(slot0 + (mi & 1) * 8 + (lane & 7)) * row_stride + (h * HD + (mi >> 1) * 8) * sizeof(T);
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(u.qf[ks], qp + ks * 16 * sizeof(T));
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) u.o[n][0] = u.o[n][1] = u.o[n][2] = u.o[n][3] = 0.f;
+  u.m_lo = u.m_hi = 0.f;  // the maximum starts from 0 (ops.cu:137)
+  u.l_lo = u.l_hi = 0.f;
+}
+
+// One block of 16 key slots starting at ks0: S = Q K^T, bias and masks, online softmax, O += P V.
+// k_off / v_off: byte offsets of this head's k and v slices inside a staged row.
+template <typename T, int HD, bool kTableSmem>
+__device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned char* rows, int row_stride, int data_bytes,
+                                               int ks0, int k_off, int v_off, int region_bits, float qscale, int lane) {
+  const int qt = lane & 3, mi = lane >> 3;
+  float sacc[2][4];
+#pragma unroll
+  for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
+  const unsigned char* kp = rows + (size_t)(ks0 + (mi >> 1) * 8 + (lane & 7)) * row_stride + k_off + (mi & 1) * 8 * sizeof(T);
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+    uint32_t kf[4];
+    ldmatrix_x4(kf, kp + ks * 16 * sizeof(T));
+    mma16816<T>(sacc[0], u.qf[ks], kf[0], kf[1]);
+    mma16816<T>(sacc[1], u.qf[ks], kf[2], kf[3]);
+  }
+  // scores -> log2 domain, bias, masks
+  float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int ks = ks0 + n * 8 + qt * 2 + e;  // key slot of this column
+      const int2 km = *reinterpret_cast<const int2*>(rows + (size_t)ks * row_stride + data_bytes);
+      // one XOR per (query row, key) tells both: same window (bits 5..11), same region (bits 0..4)
+      const int x_lo = km.y ^ u.me_lo_y, x_hi = km.y ^ u.me_hi_y;
+      const bool ok_lo = (x_lo & kMmaWindowBits) == 0, ok_hi = (x_hi & kMmaWindowBits) == 0;
+      const float madd_lo = (x_lo & region_bits) ? -100.0f * kLog2e : 0.f;
+      const float madd_hi = (x_hi & region_bits) ? -100.0f * kLog2e : 0.f;
+      const float b_lo = kTableSmem ? *reinterpret_cast<const float*>(u.tab_lo - km.x)
+                                    : __ldg(reinterpret_cast<const float*>(u.tab_lo - km.x)) * kLog2e;
+      const float b_hi = kTableSmem ? *reinterpret_cast<const float*>(u.tab_hi - km.x)
+                                    : __ldg(reinterpret_cast<const float*>(u.tab_hi - km.x)) * kLog2e;
+      float s_lo = fmaf(sacc[n][e], qscale, b_lo) + madd_lo;
+      float s_hi = fmaf(sacc[n][2 + e], qscale, b_hi) + madd_hi;
+      s_lo = ok_lo ? s_lo : -INFINITY;
+      s_hi = ok_hi ? s_hi : -INFINITY;
+      sacc[n][e] = s_lo;
+      sacc[n][2 + e] = s_hi;
+      mx_lo = fmaxf(mx_lo, s_lo);
+      mx_hi = fmaxf(mx_hi, s_hi);
+    }
+  }
+  mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+  mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+  mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+  mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+  if (mx_lo > u.m_lo) {
+    const float corr = fast_exp2(u.m_lo - mx_lo);
+    u.l_lo *= corr;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { u.o[n][0] *= corr; u.o[n][1] *= corr; }
+    u.m_lo = mx_lo;
+  }
+  if (mx_hi > u.m_hi) {
+    const float corr = fast_exp2(u.m_hi - mx_hi);
+    u.l_hi *= corr;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { u.o[n][2] *= corr; u.o[n][3] *= corr; }
+    u.m_hi = mx_hi;
+  }
+  // P in the A-fragment layout of the next MMA
+  const float p00 = fast_exp2(sacc[0][0] - u.m_lo), p01 = fast_exp2(sacc[0][1] - u.m_lo);
+  const float p02 = fast_exp2(sacc[0][2] - u.m_hi), p03 = fast_exp2(sacc[0][3] - u.m_hi);
+  const float p10 = fast_exp2(sacc[1][0] - u.m_lo), p11 = fast_exp2(sacc[1][1] - u.m_lo);
+  const float p12 = fast_exp2(sacc[1][2] - u.m_hi), p13 = fast_exp2(sacc[1][3] - u.m_hi);
+  u.l_lo += (p00 + p01) + (p10 + p11);
+  u.l_hi += (p02 + p03) + (p12 + p13);
+  uint32_t pf[4];
+  pf[0] = pack2<T>(p00, p01);
+  pf[1] = pack2<T>(p02, p03);
+  pf[2] = pack2<T>(p10, p11);
+  pf[3] = pack2<T>(p12, p13);
+  const unsigned char* vp = rows + (size_t)(ks0 + (mi & 1) * 8 + (lane & 7)) * row_stride + v_off + (mi >> 1) * 8 * sizeof(T);
+#pragma unroll
+  for (int n = 0; n < HD / 8; n += 2) {
+    uint32_t vf[4];
+    ldmatrix_x4_trans(vf, vp + n * 8 * sizeof(T));
+    mma16816<T>(u.o[n], pf, vf[0], vf[1]);
+    mma16816<T>(u.o[n + 1], pf, vf[2], vf[3]);
+  }
+}
+
+// Normalise the unit's output, park it in the q slice the unit was read from and copy the tile's
+// 16 x HD outputs to the voxels' rows with 16-byte stores (bulk stores of whole rows were tried;
+// one bulk operation per row is what bounds them).  `svox`: voxel of every slot, -1 for unused.
+template <typename T, int HD>
+__device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, unsigned char* rows, int row_stride, const int* svox,
+                                            int slot0, int h, int C, T* out, int lane) {
+  const int qr = lane >> 2, qt = lane & 3;
+  // row sums live in four lanes each
+  float ll = u.l_lo, lh = u.l_hi;
+  ll += __shfl_xor_sync(0xffffffffu, ll, 1);
+  ll += __shfl_xor_sync(0xffffffffu, ll, 2);
+  lh += __shfl_xor_sync(0xffffffffu, lh, 1);
+  lh += __shfl_xor_sync(0xffffffffu, lh, 2);
+  const float inv_lo = 1.0f / (ll + 1e-8f), inv_hi = 1.0f / (lh + 1e-8f);  // ops.cu:164
+  uint32_t* out_lo = reinterpret_cast<uint32_t*>(rows + (size_t)(slot0 + qr) * row_stride + (h * HD) * sizeof(T)) + qt;
+  uint32_t* out_hi = reinterpret_cast<uint32_t*>(rows + (size_t)(slot0 + qr + 8) * row_stride + (h * HD) * sizeof(T)) + qt;
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) {
+    out_lo[n * 4] = pack2<T>(u.o[n][0] * inv_lo, u.o[n][1] * inv_lo);
+    out_hi[n * 4] = pack2<T>(u.o[n][2] * inv_hi, u.o[n][3] * inv_hi);
+  }
+  __syncwarp();
+  constexpr int kChunks = HD / 8;  // 16-byte chunks per row segment
+  for (int idx = lane; idx < 16 * kChunks; idx += 32) {
+    const int rr = idx / kChunks, cc = idx - rr * kChunks;
+    const int slot = slot0 + rr;
+    const int v = svox[slot];
+    if (v >= 0)
+      *reinterpret_cast<uint4*>(out + (int64_t)v * C + h * HD + cc * 8) =
+          *reinterpret_cast<const uint4*>(rows + (size_t)slot * row_stride + (h * HD + cc * 8) * sizeof(T));
+  }
+}
+
+template <typename T, int HD, bool kTableSmem>
+__global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxProducerWarps, 1) k_attn_mma(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int tile = p.tile, C = p.C, H = p.H;
   const int S = p.stages, G = p.groups;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-  uint64_t* empty = full + kMaxStages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);  // phase 1: data of a stage landed
+  uint64_t* empty = full + kMaxStages;                  // phase 1: stage may be refilled
+  uint64_t* dfull = empty + kMaxStages;                 // phase 2: key tile landed
+  uint64_t* dempty = dfull + kMaxStages;                // phase 2: key stage may be refilled
+  uint64_t* qfull = dempty + kMaxStages;                // phase 2: query tile landed
+  uint64_t* qempty = qfull + 1;                         // phase 2: query stage may be refilled
   float* table_s = reinterpret_cast<float*>(smem + 256);
   unsigned char* stage0 = smem + 256 + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
   const float* table_base = kTableSmem ? table_s : p.table;
   const int gsize = kMmaGroupWarps * 32;
   const int n_cons = gsize * G;
+  const int n_cons_warps = G * kMmaGroupWarps;
   const bool is_producer = (int)threadIdx.x >= n_cons;
   const int lane = threadIdx.x & 31;
+  const int PW = p.prod_warps, pw = ((int)threadIdx.x - n_cons) >> 5;
   const int data_bytes = 3 * C * (int)sizeof(T);  // one staged row; its metadata follows
   const float qscale = p.scale * kLog2e;
+  const int region_bits = p.use_mask ? 31 : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full + s, p.prod_warps);       // one arrive (with its byte count) per producer warp
+      mbar_init(full + s, PW);               // one arrive (with its byte count) per producer warp
       mbar_init(empty + s, kMmaGroupWarps);  // every warp of the consuming group hands the stage back
+      mbar_init(dfull + s, PW);
+      mbar_init(dempty + s, n_cons_warps);   // every consumer warp works on every key tile
     }
+    mbar_init(qfull, PW);
+    mbar_init(qempty, n_cons_warps);
     mbar_fence_init();
   }
   // unused row slots are read as keys/values (and masked): they must hold finite numbers
@@ -90,8 +262,12 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
   grid_dependency_wait();
   if constexpr (kTableSmem) stage_table(table_s, p.table, p.table_floats);
   const int n_small = p.header[SSW_H_PACKS_SMALL];
+  const int n_items = p.header[SSW_H_PACKS];
   __syncthreads();
 
+  // ------------------------------------------------------------------------------------------
+  // Phase 1: packs
+  // ------------------------------------------------------------------------------------------
   const int my_items = n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   bool timed_out = false;
   if (is_producer) {
@@ -102,7 +278,6 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
     // The rows of an item are dealt round-robin to the producer warps: a warp submits its bulk
     // copies one lane after the other, so several warps submit several rows at a time.
     constexpr int kAhead = 3;
-    const int PW = p.prod_warps, pw = ((int)threadIdx.x - n_cons) >> 5;
     // The plan lists packs by ascending occupancy; walking the list backwards puts the long items
     // first and leaves the short ones for the tail of the kernel.
     auto item_index = [&](int k) { return n_small - 1 - ((int)blockIdx.x + k * (int)gridDim.x); };
@@ -148,14 +323,10 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
         const int slot = (lane + 32 * k) * PW + pw;
         if (slot < tile) {
           reinterpret_cast<int*>(st + kMmaStageVoxOff)[slot] = vox[0][k];
-          // Row metadata: .x = byte offset of the row's relative-position code in the bias table,
-          // .y = region | window-in-pack << 5 | table row << 12.  Unused slots form a window of their
-          // own (kMmaPadWindow) with neutral codes, so their (discarded) scores index inside the table.
+          // Unused slots form a window of their own with neutral codes, so their (discarded) scores
+          // index inside the bias table.
           *reinterpret_cast<int2*>(st + kMmaStageRowsOff + (size_t)slot * p.row_stride + data_bytes) =
-              vox[0][k] >= 0 ? make_int2(meta_rel(km[0][k]) * H * 4,
-                                         meta_region(km[0][k]) | ((km[0][k] & 1023) << 5) |
-                                             ((meta_rel(km[0][k]) + p.rel_off) << kMmaRelShift))
-                             : make_int2(0, (kMmaPadWindow << 5) | (p.rel_off << kMmaRelShift));
+              vox[0][k] >= 0 ? row_meta(km[0][k], km[0][k] & 1023, H, p.rel_off) : pad_meta(p.rel_off);
         }
       }
       const int my_rows = __popc(__ballot_sync(0xffffffffu, vox[0][0] >= 0)) + __popc(__ballot_sync(0xffffffffu, vox[0][1] >= 0));
@@ -188,12 +359,12 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
   } else {
     const int g = threadIdx.x / gsize;
     const int wg = (threadIdx.x - g * gsize) >> 5;  // warp inside the group
-    const int qr = lane >> 2, qt = lane & 3;        // fragment coordinates of this lane
     for (int i = g; i < my_items && !timed_out; i += G) {
       const int s = i % S;
       const int use = i / S;
       unsigned char* sp = stage0 + (size_t)s * p.stage_bytes;
       unsigned char* rows = sp + kMmaStageRowsOff;
+      const int* svox = reinterpret_cast<const int*>(sp + kMmaStageVoxOff);
       if (!mbar_wait_bounded(full + s, use & 1)) {
         timed_out = true;
         break;
@@ -203,173 +374,160 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * (HU == 3 ? 3 : kMaxGroup
       const int cpad = slots_of_window(c, 1);
       const int n_mt = (nwin * cpad + 15) >> 4;
       const int nkb = cpad > 16 ? cpad >> 4 : 1;  // 16-key blocks per window
-      // A unit is (16-slot tile, HU consecutive heads); the HU heads are independent instruction
-      // streams that the unrolled code interleaves, which hides the ldmatrix / MMA / exp latencies.
-      const int n_hg = H / HU;
-      for (int u = wg; u < n_mt * n_hg; u += kMmaGroupWarps) {
-        const int mt = u / n_hg, h0 = (u - mt * n_hg) * HU;
-        const int slot_lo = mt * 16 + qr, slot_hi = slot_lo + 8;
+      for (int un = wg; un < n_mt * H; un += kMmaGroupWarps) {
+        const int mt = un / H, h = un - mt * H;
         // first key slot of the window(s) this tile belongs to
         const int kbase = cpad > 16 ? (mt * 16 / cpad) * cpad : mt * 16;
-        const int2 me_lo = *reinterpret_cast<const int2*>(rows + (size_t)slot_lo * p.row_stride + data_bytes);
-        const int2 me_hi = *reinterpret_cast<const int2*>(rows + (size_t)slot_hi * p.row_stride + data_bytes);
-        const unsigned char* tab_lo =
-            reinterpret_cast<const unsigned char*>(table_base + (me_lo.y >> kMmaRelShift) * H + h0);
-        const unsigned char* tab_hi =
-            reinterpret_cast<const unsigned char*>(table_base + (me_hi.y >> kMmaRelShift) * H + h0);
-        const int mi = lane >> 3;
-        const int region_bits = p.use_mask ? 31 : 0;
-
-        uint32_t qf[HU][HD / 16][4];
-        float o[HU][HD / 8][4];
-        float m_lo[HU], m_hi[HU], l_lo[HU], l_hi[HU];
-#pragma unroll
-        for (int x = 0; x < HU; ++x) {
-          const unsigned char* qp = rows + (size_t)(mt * 16 + (mi & 1) * 8 + (lane & 7)) * p.row_stride +
-                                    ((h0 + x) * HD + (mi >> 1) * 8) * sizeof(T);
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qf[x][ks], qp + ks * 16 * sizeof(T));
-#pragma unroll
-          for (int n = 0; n < HD / 8; ++n) o[x][n][0] = o[x][n][1] = o[x][n][2] = o[x][n][3] = 0.f;
-          m_lo[x] = m_hi[x] = 0.f;  // maximum starts from 0 (ops.cu:137)
-          l_lo[x] = l_hi[x] = 0.f;
-        }
-
-        for (int kb = 0; kb < nkb; ++kb) {
-          const int ks0 = kbase + kb * 16;  // first key slot of this block
-          float sacc[HU][2][4];
-#pragma unroll
-          for (int x = 0; x < HU; ++x) {
-#pragma unroll
-            for (int n = 0; n < 2; ++n) sacc[x][n][0] = sacc[x][n][1] = sacc[x][n][2] = sacc[x][n][3] = 0.f;
-            const unsigned char* kp = rows + (size_t)(ks0 + (mi >> 1) * 8 + (lane & 7)) * p.row_stride +
-                                      (C + (h0 + x) * HD + (mi & 1) * 8) * sizeof(T);
-#pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks) {
-              uint32_t kf[4];
-              ldmatrix_x4(kf, kp + ks * 16 * sizeof(T));
-              mma16816<T>(sacc[x][0], qf[x][ks], kf[0], kf[1]);
-              mma16816<T>(sacc[x][1], qf[x][ks], kf[2], kf[3]);
-            }
-          }
-          // scores -> log2 domain, bias, masks (key metadata is shared by the HU heads)
-          float mx_lo[HU], mx_hi[HU];
-#pragma unroll
-          for (int x = 0; x < HU; ++x) mx_lo[x] = mx_hi[x] = -INFINITY;
-#pragma unroll
-          for (int n = 0; n < 2; ++n) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int ks = ks0 + n * 8 + qt * 2 + e;  // key slot of this column
-              const int2 km = *reinterpret_cast<const int2*>(rows + (size_t)ks * p.row_stride + data_bytes);
-              // one XOR per (query row, key) tells both: same window (bits 5..11), same region (bits 0..4)
-              const int x_lo = km.y ^ me_lo.y, x_hi = km.y ^ me_hi.y;
-              const bool ok_lo = (x_lo & kMmaWindowBits) == 0, ok_hi = (x_hi & kMmaWindowBits) == 0;
-              const float madd_lo = (x_lo & region_bits) ? -100.0f * kLog2e : 0.f;
-              const float madd_hi = (x_hi & region_bits) ? -100.0f * kLog2e : 0.f;
-#pragma unroll
-              for (int x = 0; x < HU; ++x) {
-                const float b_lo = kTableSmem ? *reinterpret_cast<const float*>(tab_lo - km.x + x * 4)
-                                              : __ldg(reinterpret_cast<const float*>(tab_lo - km.x + x * 4)) * kLog2e;
-                const float b_hi = kTableSmem ? *reinterpret_cast<const float*>(tab_hi - km.x + x * 4)
-                                              : __ldg(reinterpret_cast<const float*>(tab_hi - km.x + x * 4)) * kLog2e;
-                float s_lo = fmaf(sacc[x][n][e], qscale, b_lo) + madd_lo;
-                float s_hi = fmaf(sacc[x][n][2 + e], qscale, b_hi) + madd_hi;
-                s_lo = ok_lo ? s_lo : -INFINITY;
-                s_hi = ok_hi ? s_hi : -INFINITY;
-                sacc[x][n][e] = s_lo;
-                sacc[x][n][2 + e] = s_hi;
-                mx_lo[x] = fmaxf(mx_lo[x], s_lo);
-                mx_hi[x] = fmaxf(mx_hi[x], s_hi);
-              }
-            }
-          }
-          uint32_t pf[HU][4];
-#pragma unroll
-          for (int x = 0; x < HU; ++x) {
-            mx_lo[x] = fmaxf(mx_lo[x], __shfl_xor_sync(0xffffffffu, mx_lo[x], 1));
-            mx_lo[x] = fmaxf(mx_lo[x], __shfl_xor_sync(0xffffffffu, mx_lo[x], 2));
-            mx_hi[x] = fmaxf(mx_hi[x], __shfl_xor_sync(0xffffffffu, mx_hi[x], 1));
-            mx_hi[x] = fmaxf(mx_hi[x], __shfl_xor_sync(0xffffffffu, mx_hi[x], 2));
-            if (mx_lo[x] > m_lo[x]) {
-              const float corr = fast_exp2(m_lo[x] - mx_lo[x]);
-              l_lo[x] *= corr;
-#pragma unroll
-              for (int n = 0; n < HD / 8; ++n) { o[x][n][0] *= corr; o[x][n][1] *= corr; }
-              m_lo[x] = mx_lo[x];
-            }
-            if (mx_hi[x] > m_hi[x]) {
-              const float corr = fast_exp2(m_hi[x] - mx_hi[x]);
-              l_hi[x] *= corr;
-#pragma unroll
-              for (int n = 0; n < HD / 8; ++n) { o[x][n][2] *= corr; o[x][n][3] *= corr; }
-              m_hi[x] = mx_hi[x];
-            }
-            // P in the A-fragment layout of the next MMA
-            const float p00 = fast_exp2(sacc[x][0][0] - m_lo[x]), p01 = fast_exp2(sacc[x][0][1] - m_lo[x]);
-            const float p02 = fast_exp2(sacc[x][0][2] - m_hi[x]), p03 = fast_exp2(sacc[x][0][3] - m_hi[x]);
-            const float p10 = fast_exp2(sacc[x][1][0] - m_lo[x]), p11 = fast_exp2(sacc[x][1][1] - m_lo[x]);
-            const float p12 = fast_exp2(sacc[x][1][2] - m_hi[x]), p13 = fast_exp2(sacc[x][1][3] - m_hi[x]);
-            l_lo[x] += (p00 + p01) + (p10 + p11);
-            l_hi[x] += (p02 + p03) + (p12 + p13);
-            pf[x][0] = pack2<T>(p00, p01);
-            pf[x][1] = pack2<T>(p02, p03);
-            pf[x][2] = pack2<T>(p10, p11);
-            pf[x][3] = pack2<T>(p12, p13);
-          }
-#pragma unroll
-          for (int x = 0; x < HU; ++x) {
-            const unsigned char* vp = rows + (size_t)(ks0 + (mi & 1) * 8 + (lane & 7)) * p.row_stride +
-                                      (2 * C + (h0 + x) * HD + (mi >> 1) * 8) * sizeof(T);
-#pragma unroll
-            for (int n = 0; n < HD / 8; n += 2) {
-              uint32_t vf[4];
-              ldmatrix_x4_trans(vf, vp + n * 8 * sizeof(T));
-              mma16816<T>(o[x][n], pf[x], vf[0], vf[1]);
-              mma16816<T>(o[x][n + 1], pf[x], vf[2], vf[3]);
-            }
-          }
-        }
+        MmaUnit<HD> u;
+        unit_begin<T, HD>(u, rows, p.row_stride, data_bytes, mt * 16, h, H, table_base, lane);
+        for (int kb = 0; kb < nkb; ++kb)
+          unit_key_block<T, HD, kTableSmem>(u, rows, p.row_stride, data_bytes, kbase + kb * 16,
+                                            (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T), region_bits,
+                                            qscale, lane);
         __syncwarp();
-#pragma unroll
-        for (int x = 0; x < HU; ++x) {
-          // row sums live in four lanes each
-          float ll = l_lo[x], lh = l_hi[x];
-          ll += __shfl_xor_sync(0xffffffffu, ll, 1);
-          ll += __shfl_xor_sync(0xffffffffu, ll, 2);
-          lh += __shfl_xor_sync(0xffffffffu, lh, 1);
-          lh += __shfl_xor_sync(0xffffffffu, lh, 2);
-          const float inv_lo = 1.0f / (ll + 1e-8f), inv_hi = 1.0f / (lh + 1e-8f);  // ops.cu:164
-          // the q slice this tile was read from becomes its output slice
-          uint32_t* out_lo =
-              reinterpret_cast<uint32_t*>(rows + (size_t)slot_lo * p.row_stride + ((h0 + x) * HD) * sizeof(T)) + qt;
-          uint32_t* out_hi =
-              reinterpret_cast<uint32_t*>(rows + (size_t)slot_hi * p.row_stride + ((h0 + x) * HD) * sizeof(T)) + qt;
-#pragma unroll
-          for (int n = 0; n < HD / 8; ++n) {
-            out_lo[n * 4] = pack2<T>(o[x][n][0] * inv_lo, o[x][n][1] * inv_lo);
-            out_hi[n * 4] = pack2<T>(o[x][n][2] * inv_hi, o[x][n][3] * inv_hi);
-          }
-        }
-        // The tile's 16 x (HU*HD) outputs now sit in shared memory in row order: copy them out with
-        // 16-byte stores, a run of HU*HD elements per voxel row (bulk stores of whole rows were
-        // tried; one bulk operation per row is what bounds them).
-        __syncwarp();
-        {
-          constexpr int kChunks = HU * HD / 8;  // 16-byte chunks per row segment
-          const int* svox = reinterpret_cast<const int*>(sp + kMmaStageVoxOff);
-          for (int idx = lane; idx < 16 * kChunks; idx += 32) {
-            const int rr = idx / kChunks, cc = idx - rr * kChunks;
-            const int slot = mt * 16 + rr;
-            const int v = svox[slot];
-            if (v >= 0)
-              *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out) + (int64_t)v * C + h0 * HD + cc * 8) =
-                  *reinterpret_cast<const uint4*>(rows + (size_t)slot * p.row_stride + (h0 * HD + cc * 8) * sizeof(T));
-          }
-        }
+        unit_finish<T, HD>(u, rows, p.row_stride, svox, mt * 16, h, C, reinterpret_cast<T*>(p.out), lane);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty + s);
+    }
+  }
+  if (timed_out) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
+  // A timed-out role leaves; the other roles then time out on their own bounded waits.
+  if (__syncthreads_or(timed_out)) return;
+  if (n_items <= n_small) return;
+
+  // ------------------------------------------------------------------------------------------
+  // Phase 2: windows with c > tile.  Stage 0 holds the item's query rows (q slices), stages
+  // 1..S-1 form a ring for the window's key tiles (k|v slices).
+  // ------------------------------------------------------------------------------------------
+  const int R = S - 1;                           // key stages
+  const int n_mt_tile = tile >> 4;               // 16-row tiles per query tile
+  const int heads_per_round = n_cons_warps / n_mt_tile;
+  const int rounds = (H + heads_per_round - 1) / heads_per_round;
+  const uint32_t q_bytes = (uint32_t)C * sizeof(T), kv_bytes = 2u * C * sizeof(T);
+  unsigned char* q_stage = stage0;
+  unsigned char* q_rows = q_stage + kMmaStageRowsOff;
+  int kseq = 0, qseq = 0;  // key tiles / query tiles handled so far by this CTA
+  for (int item = n_small + blockIdx.x; item < n_items && !timed_out; item += gridDim.x, ++qseq) {
+    const int4 d = __ldg(p.pack_desc + item);
+    const int c = d.y;
+    const int q_first = (-d.z - 1) * tile;
+    const int n_q = min(tile, c - q_first);
+    const int n_kt = (c + tile - 1) / tile;
+    if (is_producer) {
+      // query tile
+      int qv[2], qm[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int slot = (lane + 32 * k) * PW + pw;
+        qv[k] = -1;
+        qm[k] = 0;
+        if (slot < n_q) {
+          qv[k] = __ldg(p.pack_perm + d.x + q_first + slot);
+          qm[k] = __ldg(p.pack_meta + d.x + q_first + slot);
+        }
+      }
+      if (qseq > 0 && !mbar_wait_bounded(qempty, (qseq - 1) & 1)) {
+        timed_out = true;
+        break;
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int slot = (lane + 32 * k) * PW + pw;
+        if (slot < tile) {
+          reinterpret_cast<int*>(q_stage + kMmaStageVoxOff)[slot] = qv[k];
+          *reinterpret_cast<int2*>(q_rows + (size_t)slot * p.row_stride + data_bytes) =
+              qv[k] >= 0 ? row_meta(qm[k], 0, H, p.rel_off) : pad_meta(p.rel_off);
+        }
+      }
+      {
+        const int my_rows = __popc(__ballot_sync(0xffffffffu, qv[0] >= 0)) + __popc(__ballot_sync(0xffffffffu, qv[1] >= 0));
+        if (lane == 0) mbar_expect_tx(qfull, (uint32_t)my_rows * q_bytes);
+        __syncwarp();
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int slot = (lane + 32 * k) * PW + pw;
+        if (slot < tile && qv[k] >= 0)
+          bulk_g2s(q_rows + (size_t)slot * p.row_stride, reinterpret_cast<const T*>(p.qkv) + (int64_t)qv[k] * 3 * C,
+                   q_bytes, qfull);
+      }
+      // key tiles, once per round of heads
+      for (int rt = 0; rt < rounds * n_kt && !timed_out; ++rt, ++kseq) {
+        const int kt = rt % n_kt;
+        const int k0 = kt * tile, n_k = min(tile, c - k0);
+        int kv[2], kmeta[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int slot = (lane + 32 * k) * PW + pw;
+          kv[k] = -1;
+          kmeta[k] = 0;
+          if (slot < n_k) {
+            kv[k] = __ldg(p.pack_perm + d.x + k0 + slot);
+            kmeta[k] = __ldg(p.pack_meta + d.x + k0 + slot);
+          }
+        }
+        const int s = 1 + kseq % R, use = kseq / R;
+        if (use > 0 && !mbar_wait_bounded(dempty + s, (use - 1) & 1)) {
+          timed_out = true;
+          break;
+        }
+        unsigned char* krows = stage0 + (size_t)s * p.stage_bytes + kMmaStageRowsOff;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int slot = (lane + 32 * k) * PW + pw;
+          if (slot < tile)
+            *reinterpret_cast<int2*>(krows + (size_t)slot * p.row_stride + data_bytes) =
+                kv[k] >= 0 ? row_meta(kmeta[k], 0, H, p.rel_off) : pad_meta(p.rel_off);
+        }
+        const int my_rows = __popc(__ballot_sync(0xffffffffu, kv[0] >= 0)) + __popc(__ballot_sync(0xffffffffu, kv[1] >= 0));
+        if (lane == 0) mbar_expect_tx(dfull + s, (uint32_t)my_rows * kv_bytes);
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int slot = (lane + 32 * k) * PW + pw;
+          if (slot < tile && kv[k] >= 0)
+            bulk_g2s(krows + (size_t)slot * p.row_stride + q_bytes,
+                     reinterpret_cast<const T*>(p.qkv) + (int64_t)kv[k] * 3 * C + C, kv_bytes, dfull + s);
+        }
+      }
+    } else {
+      const int cw = threadIdx.x >> 5;  // consumer warp
+      const int mt = cw % n_mt_tile, hsel = cw / n_mt_tile;
+      if (!mbar_wait_bounded(qfull, qseq & 1)) {
+        timed_out = true;
+        break;
+      }
+      for (int r = 0; r < rounds && !timed_out; ++r) {
+        const int h = r * heads_per_round + hsel;
+        const bool active = hsel < heads_per_round && h < H && mt * 16 < n_q;
+        MmaUnit<HD> u;
+        if (active) unit_begin<T, HD>(u, q_rows, p.row_stride, data_bytes, mt * 16, h, H, table_base, lane);
+        for (int kt = 0; kt < n_kt; ++kt, ++kseq) {
+          const int s = 1 + kseq % R, use = kseq / R;
+          if (!mbar_wait_bounded(dfull + s, use & 1)) {
+            timed_out = true;
+            break;
+          }
+          if (active) {
+            const unsigned char* krows = stage0 + (size_t)s * p.stage_bytes + kMmaStageRowsOff;
+            const int n_k = min(tile, c - kt * tile);
+            for (int kb = 0; kb * 16 < n_k; ++kb)
+              unit_key_block<T, HD, kTableSmem>(u, krows, p.row_stride, data_bytes, kb * 16,
+                                                (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
+                                                region_bits, qscale, lane);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dempty + s);
+        }
+        if (active && !timed_out) {
+          __syncwarp();
+          unit_finish<T, HD>(u, q_rows, p.row_stride, reinterpret_cast<const int*>(q_stage + kMmaStageVoxOff), mt * 16, h,
+                             C, reinterpret_cast<T*>(p.out), lane);
+        }
+      }
+      __syncwarp();
+      if (lane == 0 && !timed_out) mbar_arrive(qempty);
     }
   }
   if (timed_out) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
@@ -393,9 +551,9 @@ static MmaShape mma_shape(int tile, int heads, int head_dim, const int32_t rpb_w
   int groups = stages - 1;
   if (groups > kMaxGroups) groups = kMaxGroups;
   if (groups < 1) groups = 1;
-  if (const char* e = getenv("SSW_STAGES")) {
+  if (const char* e = getenv("SSW_STAGES")) {  // tuning overrides (experiments only)
     const int v = atoi(e);
-    if (v >= 2 && v <= stages) stages = v;
+    if (v >= 3 && v <= stages) stages = v;
   }
   if (const char* e = getenv("SSW_GROUPS")) {
     const int v = atoi(e);
@@ -416,53 +574,47 @@ int mma_default_tile(int heads, int head_dim, const int32_t rpb_window[3]) {
   return 16;
 }
 
-template <typename T, int HD, int HU>
+template <typename T, int HD>
 static int launch_mma(AttnParams p, const MmaShape& s, cudaStream_t stream) {
   int dev = 0, sms = 0;
   SSW_CUDA_TRY(cudaGetDevice(&dev));
   SSW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  if (HU == 3 && p.groups > 3) p.groups = 3;  // three interleaved heads need the larger register budget
-  p.prod_warps = 4;  // 576-byte rows: the copy submission rate, not the bytes, bounds the producer
+  p.prod_warps = 4;  // 16-bit rows are short: the copy submission rate, not the bytes, bounds the producer
   if (const char* e = getenv("SSW_PROD_WARPS")) {  // tuning override (experiments only)
     const int v = atoi(e);
     if (v >= 1 && v <= kMaxProducerWarps) p.prod_warps = v;
   }
   const int threads = p.groups * kMmaGroupWarps * 32 + 32 * p.prod_warps;
   if (s.table_floats > 0) {
-    auto kern = k_attn_mma<T, HD, HU, true>;
+    auto kern = k_attn_mma<T, HD, true>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem));
     SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), s.smem, stream, p));
   } else {
-    auto kern = k_attn_mma<T, HD, HU, false>;
+    auto kern = k_attn_mma<T, HD, false>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem));
     SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), s.smem, stream, p));
   }
   return SSW_OK;
 }
 
-// One head per consumer unit: interleaving two or three heads in a unit was measured slower (more
-// registers, fewer units to spread over the warps of a group).
-template <typename T, int HD>
-static int launch_mma_heads(const AttnParams& p, const MmaShape& s, cudaStream_t stream) {
-  return launch_mma<T, HD, 1>(p, s, stream);
-}
-
-// Packs of a padded plan, 16-bit inputs.  `p` arrives with the plan pointers, qkv/out/table, H, C,
-// tile, scale, use_mask and rel_off filled in.
+// Padded plan, 16-bit inputs: packs and larger windows.  `p` arrives with the plan pointers,
+// qkv/out/table, H, C, tile, scale, use_mask and rel_off filled in.
 int run_attn_mma(AttnParams p, int dtype, int head_dim, const int32_t rpb_window[3], cudaStream_t stream) {
   const MmaShape s = mma_shape(p.tile, p.H, head_dim, rpb_window);
-  if (s.stages < 2 || s.smem > 227 * 1024) return SSW_E_UNSUPPORTED;
+  // three stages at least: the second phase keeps the query tile in one and needs two for key tiles
+  if (s.stages < 3 || s.smem > 227 * 1024) return SSW_E_UNSUPPORTED;
+  if (p.tile & 15) return SSW_E_INVALID;
   p.groups = s.groups;
   p.stages = s.stages;
   p.row_stride = s.row_stride;
   p.stage_bytes = s.stage_bytes;
   p.table_floats = s.table_floats;
   if (dtype == SSW_BF16) {
-    if (head_dim == 16) return launch_mma_heads<__nv_bfloat16, 16>(p, s, stream);
-    if (head_dim == 32) return launch_mma_heads<__nv_bfloat16, 32>(p, s, stream);
+    if (head_dim == 16) return launch_mma<__nv_bfloat16, 16>(p, s, stream);
+    if (head_dim == 32) return launch_mma<__nv_bfloat16, 32>(p, s, stream);
   } else if (dtype == SSW_F16) {
-    if (head_dim == 16) return launch_mma_heads<__half, 16>(p, s, stream);
-    if (head_dim == 32) return launch_mma_heads<__half, 32>(p, s, stream);
+    if (head_dim == 16) return launch_mma<__half, 16>(p, s, stream);
+    if (head_dim == 32) return launch_mma<__half, 32>(p, s, stream);
   }
   return SSW_E_UNSUPPORTED;
 }

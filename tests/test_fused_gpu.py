@@ -97,7 +97,7 @@ def test_fused_half_types(dtype, tol):
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, BF16_TOL), (torch.float16, 3e-3)])
 def test_fused_shapes(n_vox, grid, heads, hd, window, shift, dtype, tol):
     """fp32 runs the CUDA-core kernel on a contiguous plan, the 16-bit types the tensor-core kernel
-    on a padded plan (windows above one pack fall through to the CUDA-core kernel's second phase)."""
+    on a padded plan (windows above one pack take that kernel's second phase: key tiles streamed past a resident query tile)."""
     from sparseswin3d_b200 import attention
 
     dev = torch.device("cuda:0")
