@@ -655,10 +655,8 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   if ((head_dim * elt) % 16) return SSW_E_UNSUPPORTED;
   const int tile = L->tile_rows;
   if (tile > kMaxTile) return SSW_E_UNSUPPORTED;
-  const KernelShape s = kernel_shape(tile, heads, head_dim, elt, rpb_window);
-  if (s.stages < 2 || s.smem > 227 * 1024) return SSW_E_UNSUPPORTED;
-  const int threads = s.groups * s.group_threads + 32 * s.prod_warps;
-  AttnParams p;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  AttnParams p = {};
   p.qkv = qkv;
   p.out = out;
   p.attn_vals = attn_vals;
@@ -674,23 +672,25 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   p.H = heads;
   p.C = C;
   p.tile = tile;
-  p.HG = s.hg;
-  p.group_threads = s.group_threads;
-  p.groups = s.groups;
-  p.stages = s.stages;
-  p.prod_warps = s.prod_warps;
   p.scale = scale;
   p.use_mask = use_mask;
-  p.row_stride = s.row_stride;
-  p.stage_bytes = s.stage_bytes;
-  p.out_off = s.out_off;
-  p.table_floats = s.table_floats;
-  cudaStream_t stream = (cudaStream_t)stream_;
   if (L->padded) {
     // padded plan: the tensor-core kernel takes both the packs and the windows beyond a pack
     if (elt != 2 || attn_vals) return SSW_E_INVALID;
     return run_attn_mma(p, dtype, head_dim, rpb_window, stream);
   }
+  const KernelShape s = kernel_shape(tile, heads, head_dim, elt, rpb_window);
+  if (s.stages < 2 || s.smem > 227 * 1024) return SSW_E_UNSUPPORTED;
+  const int threads = s.groups * s.group_threads + 32 * s.prod_warps;
+  p.HG = s.hg;
+  p.group_threads = s.group_threads;
+  p.groups = s.groups;
+  p.stages = s.stages;
+  p.prod_warps = s.prod_warps;
+  p.row_stride = s.row_stride;
+  p.stage_bytes = s.stage_bytes;
+  p.out_off = s.out_off;
+  p.table_floats = s.table_floats;
   switch (dtype) {
     case SSW_F32: return dispatch<float>(p, head_dim, threads, s.smem, stream);
     case SSW_BF16: return dispatch<__nv_bfloat16>(p, head_dim, threads, s.smem, stream);

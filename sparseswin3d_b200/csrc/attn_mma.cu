@@ -177,6 +177,17 @@ __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned ch
   pf[1] = pack2<T>(p02, p03);
   pf[2] = pack2<T>(p10, p11);
   pf[3] = pack2<T>(p12, p13);
+  // bf16 keeps 8 bits of a probability: too coarse for rows that sum many keys or cancel.  The
+  // rounding residual goes through a second MMA (the tensor pipe is far from busy), which leaves the
+  // output rounding as the only 16-bit step after the scores.
+  constexpr bool kSplitP = std::is_same<T, __nv_bfloat16>::value;
+  uint32_t pl[4];
+  if constexpr (kSplitP) {
+    pl[0] = pack2<T>(p00 - __uint_as_float(pf[0] << 16), p01 - __uint_as_float(pf[0] & 0xffff0000u));
+    pl[1] = pack2<T>(p02 - __uint_as_float(pf[1] << 16), p03 - __uint_as_float(pf[1] & 0xffff0000u));
+    pl[2] = pack2<T>(p10 - __uint_as_float(pf[2] << 16), p11 - __uint_as_float(pf[2] & 0xffff0000u));
+    pl[3] = pack2<T>(p12 - __uint_as_float(pf[3] << 16), p13 - __uint_as_float(pf[3] & 0xffff0000u));
+  }
   const unsigned char* vp = rows + (size_t)(ks0 + (mi & 1) * 8 + (lane & 7)) * row_stride + v_off + (mi >> 1) * 8 * sizeof(T);
 #pragma unroll
   for (int n = 0; n < HD / 8; n += 2) {
@@ -184,6 +195,10 @@ __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned ch
     ldmatrix_x4_trans(vf, vp + n * 8 * sizeof(T));
     mma16816<T>(u.o[n], pf, vf[0], vf[1]);
     mma16816<T>(u.o[n + 1], pf, vf[2], vf[3]);
+    if constexpr (kSplitP) {
+      mma16816<T>(u.o[n], pl, vf[0], vf[1]);
+      mma16816<T>(u.o[n + 1], pl, vf[2], vf[3]);
+    }
   }
 }
 

@@ -132,3 +132,34 @@ def test_padded_plan_is_rejected_for_fp32_and_coo_output():
     a = attention.window_attention_fused(case["qkv"].to(dev).bfloat16(), plan, case["table"].to(dev), case["scale"])
     b = attention.window_attention_fused(case["qkv"].to(dev).bfloat16(), plan2, case["table"].to(dev), case["scale"])
     assert rel_err(a.float().cpu(), b.float().cpu()) <= BF16_TOL
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, BF16_TOL), (torch.float32, FP32_TOL)])
+def test_skewed_occupancy_window9(dtype, tol):
+    """The skewed-occupancy stress shape at reduced size: half the 9^3 windows are completely full
+    (729 voxels, far above a tile), the rest hold 1-8 voxels; C = 192, 6 heads x 32, shifted and
+    masked.  16-bit runs both phases of the tensor-core kernel with the bias table in global
+    memory (17^3 x 6 entries do not fit next to the stages)."""
+    import numpy as np
+
+    from sparseswin3d_b200 import attention, scenes, window
+
+    dev = torch.device("cuda:0")
+    H, hd, W, shift = 6, 32, (9, 9, 9), (4, 4, 4)
+    coords_np, dims = scenes.skewed_scene(grid=27, window=9, p_dense=0.5, seed=3)
+    coords = torch.from_numpy(coords_np)
+    N = coords.shape[0]
+    idx, Bw, n, ws, ss, dp = O.window_keys(coords, 1, dims, W, shift)
+    mask = O.compute_mask(dp, ws, ss)
+    g = torch.Generator().manual_seed(7)
+    qkv = torch.randn(N, 3, H, hd, generator=g).to(dtype)
+    table = torch.randn(17 ** 3, H, generator=g) * 0.5
+    ref = O.dense_window_attention(qkv.float(), idx, hd ** -0.5, table, O.relative_position_index(W), mask)
+    geom = window.resolve_geometry(1, dims, W, shift)
+    plan = window.bucket_windows(coords=coords.to(dev), geom=geom, **attention.plan_params(H, hd, dtype, W))
+    out = attention.window_attention_fused(qkv.to(dev), plan, table.to(dev), hd ** -0.5, use_mask=True)
+    st = plan.stats()
+    assert st["error"] == 0 and st["c_max"] > 64 and st["voxels"] == N
+    counts = np.unique(idx[:, 0].numpy(), return_counts=True)[1]
+    assert st["sum_c2"] == int((counts.astype(np.int64) ** 2).sum())
+    assert rel_err(out.float().cpu(), ref) <= tol
