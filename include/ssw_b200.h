@@ -133,8 +133,9 @@ typedef struct ssw_plan_layout {
  * from ssw_default_tile_rows / ssw_default_padded for the configuration. */
 int ssw_plan_layout_init(ssw_plan_layout* L, int64_t n_vox, int32_t n_windows, int32_t n_per_window,
                          int32_t tile_rows, int32_t padded);
-/* The default tile_rows for a configuration (host only): the largest tile whose two pipeline
- * stages, plus the bias table when it is small enough to stage, let two CTAs share an SM. */
+/* The default tile_rows for a configuration (host only): the largest tile that leaves three
+ * (fp32, CUDA-core kernel) or four (16-bit, tensor-core kernel) pipeline stages in one SM's shared
+ * memory next to the bias table, when that is small enough to be staged there. */
 int32_t ssw_default_tile_rows(int32_t heads, int32_t head_dim, int dtype, const int32_t rpb_window[3]);
 /* 1 when ssw_attn_fused serves this dtype with the tensor-core kernel (bf16, fp16), else 0. */
 int32_t ssw_default_padded(int dtype);
@@ -182,7 +183,9 @@ int ssw_bucket_windows_static(const int32_t* coords, const ssw_geometry* geom,
  *   out   [N, heads*head_dim] of `dtype`, rows in the caller's voxel order
  *   attn_vals (may be NULL) receives the post-softmax COO values in upstream order
  *         (window, head, pos_i, pos_j), sum c^2 * heads elements of `dtype`.
- * use_mask != 0 applies the -100 shift mask from the region ids stored in the plan. */
+ * use_mask != 0 applies the -100 shift mask from the region ids stored in the plan.
+ * A contiguous plan runs the CUDA-core kernel (any dtype); a padded plan runs the tensor-core
+ * kernel (bf16 / fp16 only, attn_vals must be NULL, SSW_E_INVALID otherwise). */
 int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t head_dim,
                    const ssw_plan_layout* L, const int32_t* plan,
                    const float* table, const int32_t rpb_window[3], float scale, int use_mask,

@@ -62,9 +62,8 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 
 // Stage the relative-position bias table in shared memory, pre-multiplied by log2(e).  Loads are
 // issued eight at a time so that the loop is bound by bandwidth, not by one L2 round trip per value.
-__device__ __forceinline__ void stage_table(float* dst, const float* __restrict__ src, int n) {
-  const int step = blockDim.x;
-  for (int i0 = threadIdx.x; i0 < n; i0 += step * 8) {
+__device__ __forceinline__ void stage_table(float* dst, const float* __restrict__ src, int n, int tid, int step) {
+  for (int i0 = tid; i0 < n; i0 += step * 8) {
     float v[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) v[k] = (i0 + k * step < n) ? __ldg(src + i0 + k * step) : 0.f;
@@ -73,6 +72,10 @@ __device__ __forceinline__ void stage_table(float* dst, const float* __restrict_
       if (i0 + k * step < n) dst[i0 + k * step] = v[k] * kLog2e;
   }
 }
+
+// Hardware barrier 1 over the first `n` threads of the CTA (the consumers): the producers do not
+// take part, so they can start gathering rows while the consumers stage the bias table.
+__device__ __forceinline__ void consumer_sync(int n) { asm volatile("bar.sync 1, %0;" ::"r"(n) : "memory"); }
 
 // Barrier among the warps of one consumer group, built on an mbarrier so that the wait is bounded.
 __device__ __forceinline__ bool group_barrier(uint64_t* bar, uint32_t& phase, int lane) {

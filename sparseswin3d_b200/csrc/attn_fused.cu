@@ -5,17 +5,19 @@
 // either *packs* of windows that all hold exactly c voxels (c <= tile) or query tiles of a window
 // with c > tile.
 //
-// Phase A (packs).  CTA b owns items b, b+grid, ...; item i uses pipeline stage i % S and is
-// computed by consumer group i % G.  One producer warp runs ahead: it reads the item descriptor
-// and the voxel ids of the item's rows and gathers the whole q|k|v rows (3*C contiguous elements
-// each) into the stage with one 1-D bulk (TMA) copy per voxel, completing on the stage's `full`
-// mbarrier.  The bias table lives in shared memory.  In a consumer group, thread (hg, r) owns
-// query row r for heads hg, hg+HG, ...: q comes from the staged row, the thread walks the keys of
-// its own window with a chunked online softmax in the log2 domain (dot products and the P.V
-// update are packed fp32 FMAs, fma.rn.f32x2), and writes its output slice back into the stage.
-// Each thread writes its output slice straight to global memory and the group's warps hand the
-// stage back through `empty`.  16-bit inputs are copied into the upper half of each fp32 row and
-// widened in place once per item.
+// Phase A (packs).  CTA b owns every grid-th item of the pack list, walked from its heavy end;
+// item i uses pipeline stage i % S and is computed by consumer group i % G.  The producer warps
+// run ahead: they read the item descriptor and the voxel ids of the item's rows (prefetched a few
+// items ahead in registers) and gather the whole q|k|v rows (3*C contiguous elements each) into
+// the stage with one 1-D bulk (TMA) copy per voxel, completing on the stage's `full` mbarrier;
+// the rows of an item are dealt round-robin to the producer warps, because a warp submits its
+// copies one lane after the other.  The bias table lives in shared memory, staged by the consumers
+// while the producers already gather.  In a consumer group, thread (hg, r) owns query row r for
+// heads hg, hg+HG, ...: q comes from the staged row, the thread walks the keys of its own window
+// with a chunked online softmax in the log2 domain (dot products and the P.V update are packed
+// fp32 FMAs, fma.rn.f32x2) and writes its output slice straight to global memory; the group's
+// warps hand the stage back through `empty`.  16-bit inputs are copied into the upper half of
+// each fp32 row and widened in place once per item.
 //
 // Phase B (windows with c > tile): the same arithmetic, one query tile per item, key tiles
 // streamed through stage 0 without overlap; q and the output go straight through global memory.
@@ -32,7 +34,7 @@
 namespace ssw {
 
 // Shared memory: [barriers 256 B][bias table][stage 0][stage 1]...
-// Stage: [desc int4][vox int[kMaxTile]][rows tile*row_stride][16-bit out staging]
+// Stage: [desc int4][vox int[kMaxTile]][rows tile*row_stride]
 // Row:   [q | k | v as 3*C floats][meta int2 {byte offset of the key's bias-table row,
 //         region | (query-side relative-position code << 8)}][8 B unused]
 // The 16 bytes after the data skew consecutive rows across the shared-memory banks and carry the
@@ -290,13 +292,18 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     mbar_init(bbar, 1);
     mbar_fence_init();
   }
+  __syncthreads();
   // Only the barrier set-up may run ahead of the kernel this launch is chained behind: the plan,
   // qkv and the bias table may all have been written by it.
   grid_dependency_wait();
   const int n_small = p.header[SSW_H_PACKS_SMALL];
   const int n_items = p.header[SSW_H_PACKS];
-  if constexpr (kTableSmem) stage_table(table_s, p.table, p.table_floats);
-  __syncthreads();
+  if constexpr (kTableSmem) {
+    if (!is_producer) {  // the producers are already gathering the first items
+      stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons);
+      consumer_sync(n_cons);
+    }
+  }
 
   // ------------------------------------------------------------------------------------------
   // Phase A: packs, producer / consumer pipeline

@@ -105,9 +105,9 @@ __device__ __forceinline__ void unit_begin(MmaUnit<HD>& u, const unsigned char* 
 
 // One block of 16 key slots starting at ks0: S = Q K^T, bias and masks, online softmax, O += P V.
 // k_off / v_off: byte offsets of this head's k and v slices inside a staged row.
-template <typename T, int HD, bool kTableSmem>
+template <typename T, int HD, bool kTableSmem, bool kMask>
 __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned char* rows, int row_stride, int data_bytes,
-                                               int ks0, int k_off, int v_off, int region_bits, float qscale, int lane) {
+                                               int ks0, int k_off, int v_off, float qscale, int lane) {
   const int qt = lane & 3, mi = lane >> 3;
   float sacc[2][4];
 #pragma unroll
@@ -131,8 +131,8 @@ __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned ch
       // one XOR per (query row, key) tells both: same window (bits 5..11), same region (bits 0..4)
       const int x_lo = km.y ^ u.me_lo_y, x_hi = km.y ^ u.me_hi_y;
       const bool ok_lo = (x_lo & kMmaWindowBits) == 0, ok_hi = (x_hi & kMmaWindowBits) == 0;
-      const float madd_lo = (x_lo & region_bits) ? -100.0f * kLog2e : 0.f;
-      const float madd_hi = (x_hi & region_bits) ? -100.0f * kLog2e : 0.f;
+      const float madd_lo = (kMask && (x_lo & 31)) ? -100.0f * kLog2e : 0.f;
+      const float madd_hi = (kMask && (x_hi & 31)) ? -100.0f * kLog2e : 0.f;
       const float b_lo = kTableSmem ? *reinterpret_cast<const float*>(u.tab_lo - km.x)
                                     : __ldg(reinterpret_cast<const float*>(u.tab_lo - km.x)) * kLog2e;
       const float b_hi = kTableSmem ? *reinterpret_cast<const float*>(u.tab_hi - km.x)
@@ -235,7 +235,7 @@ __device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, unsigned char*
   }
 }
 
-template <typename T, int HD, bool kTableSmem>
+template <typename T, int HD, bool kTableSmem, bool kMask>
 __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxProducerWarps, 1) k_attn_mma(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int tile = p.tile, C = p.C, H = p.H;
@@ -257,7 +257,6 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   const int PW = p.prod_warps, pw = ((int)threadIdx.x - n_cons) >> 5;
   const int data_bytes = 3 * C * (int)sizeof(T);  // one staged row; its metadata follows
   const float qscale = p.scale * kLog2e;
-  const int region_bits = p.use_mask ? 31 : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -274,11 +273,16 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   for (int i = threadIdx.x; i < (S * p.stage_bytes) / 16; i += blockDim.x)
     reinterpret_cast<uint4*>(stage0)[i] = make_uint4(0, 0, 0, 0);
   fence_async_smem();  // order the zero fill before the bulk copies that will land in the same rows
+  __syncthreads();
   grid_dependency_wait();
-  if constexpr (kTableSmem) stage_table(table_s, p.table, p.table_floats);
   const int n_small = p.header[SSW_H_PACKS_SMALL];
   const int n_items = p.header[SSW_H_PACKS];
-  __syncthreads();
+  if constexpr (kTableSmem) {
+    if (!is_producer) {  // the producers are already gathering the first items
+      stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons);
+      consumer_sync(n_cons);
+    }
+  }
 
   // ------------------------------------------------------------------------------------------
   // Phase 1: packs
@@ -396,9 +400,9 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
         MmaUnit<HD> u;
         unit_begin<T, HD>(u, rows, p.row_stride, data_bytes, mt * 16, h, H, table_base, lane);
         for (int kb = 0; kb < nkb; ++kb)
-          unit_key_block<T, HD, kTableSmem>(u, rows, p.row_stride, data_bytes, kbase + kb * 16,
-                                            (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T), region_bits,
-                                            qscale, lane);
+          unit_key_block<T, HD, kTableSmem, kMask>(u, rows, p.row_stride, data_bytes, kbase + kb * 16,
+                                                   (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
+                                                   qscale, lane);
         __syncwarp();
         unit_finish<T, HD>(u, rows, p.row_stride, svox, mt * 16, h, C, reinterpret_cast<T*>(p.out), lane);
       }
@@ -528,9 +532,9 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
             const unsigned char* krows = stage0 + (size_t)s * p.stage_bytes + kMmaStageRowsOff;
             const int n_k = min(tile, c - kt * tile);
             for (int kb = 0; kb * 16 < n_k; ++kb)
-              unit_key_block<T, HD, kTableSmem>(u, krows, p.row_stride, data_bytes, kb * 16,
-                                                (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
-                                                region_bits, qscale, lane);
+              unit_key_block<T, HD, kTableSmem, kMask>(u, krows, p.row_stride, data_bytes, kb * 16,
+                                                       (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
+                                                       qscale, lane);
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(dempty + s);
@@ -600,15 +604,12 @@ static int launch_mma(AttnParams p, const MmaShape& s, cudaStream_t stream) {
     if (v >= 1 && v <= kMaxProducerWarps) p.prod_warps = v;
   }
   const int threads = p.groups * kMmaGroupWarps * 32 + 32 * p.prod_warps;
-  if (s.table_floats > 0) {
-    auto kern = k_attn_mma<T, HD, true>;
-    SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem));
-    SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), s.smem, stream, p));
-  } else {
-    auto kern = k_attn_mma<T, HD, false>;
-    SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem));
-    SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), s.smem, stream, p));
-  }
+  // four variants: bias table in shared memory or not, shift mask or not
+  void (*kern)(AttnParams) =
+      s.table_floats > 0 ? (p.use_mask ? k_attn_mma<T, HD, true, true> : k_attn_mma<T, HD, true, false>)
+                         : (p.use_mask ? k_attn_mma<T, HD, false, true> : k_attn_mma<T, HD, false, false>);
+  SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem));
+  SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), s.smem, stream, p));
   return SSW_OK;
 }
 

@@ -125,7 +125,7 @@ def bucket_windows(*, coords: Optional[torch.Tensor] = None, geom: Optional[Geom
                    indices: Optional[torch.Tensor] = None, n_windows: Optional[int] = None,
                    n_per_window: Optional[int] = None, mask: Optional[torch.Tensor] = None,
                    rpb_window: Sequence[int] = (7, 7, 7), tile_rows: int = 64, padded: bool = False,
-                   scratch: Optional[torch.Tensor] = None) -> WindowPlan:
+                   scratch: Optional[torch.Tensor] = None, plan_buffer: Optional[torch.Tensor] = None) -> WindowPlan:
     """Sort voxels by (window, pos) on the device and build the fused kernel's work list.
 
     Give either ``coords`` [N,4] + ``geom`` (pad, cyclic shift, partition and region ids are
@@ -134,7 +134,9 @@ def bucket_windows(*, coords: Optional[torch.Tensor] = None, geom: Optional[Geom
     x.spatial_shape[0]) with an optional ``mask`` [nW, n] int8 from compute_mask.
 
     ``tile_rows`` and ``padded`` shape the fused kernel's work list; take them from
-    ``attention.plan_params(heads, head_dim, dtype, window)`` for the tensor the plan will serve."""
+    ``attention.plan_params(heads, head_dim, dtype, window)`` for the tensor the plan will serve.
+    ``scratch`` and ``plan_buffer`` (int32 device tensors, reused when large enough) let a caller
+    that builds plans repeatedly keep the call free of allocations."""
     if (coords is None) == (indices is None):
         raise _lib.SswError("give exactly one of coords= or indices=")
     if coords is not None:
@@ -157,7 +159,12 @@ def bucket_windows(*, coords: Optional[torch.Tensor] = None, geom: Optional[Geom
     check(lib.ssw_plan_layout_init(L, src.shape[0], int(n_windows), int(n_per_window), int(tile_rows), int(bool(padded))),
           "ssw_plan_layout_init")
     dev = src.device
-    plan = torch.empty(L.plan_ints, dtype=torch.int32, device=dev)
+    if plan_buffer is not None and plan_buffer.numel() >= L.plan_ints:
+        if plan_buffer.dtype != torch.int32 or plan_buffer.device != dev or not plan_buffer.is_contiguous():
+            raise _lib.SswError("plan_buffer must be a contiguous int32 tensor on the same device")
+        plan = plan_buffer[: L.plan_ints]
+    else:
+        plan = torch.empty(L.plan_ints, dtype=torch.int32, device=dev)
     if scratch is None or scratch.numel() < L.scratch_ints:
         scratch = torch.empty(max(L.scratch_ints, 1), dtype=torch.int32, device=dev)
     rw = (_lib.i32 * 3)(*[int(x) for x in rpb_window])
