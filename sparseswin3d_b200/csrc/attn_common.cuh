@@ -62,8 +62,18 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 
 // Stage the relative-position bias table in shared memory, pre-multiplied by log2(e).  Loads are
 // issued eight at a time so that the loop is bound by bandwidth, not by one L2 round trip per value.
-__device__ __forceinline__ void stage_table(float* dst, const float* __restrict__ src, int n, int tid, int step) {
-  for (int i0 = tid; i0 < n; i0 += step * 8) {
+// Stage the bias table in shared memory, pre-multiplied by log2 e.  Called by the first `step`
+// threads of the CTA (tid = 0..step-1).  When the table starts on a 16-byte boundary its bulk
+// comes in with one bulk (TMA) copy completing on `bar` (initialised with count 1) and is scaled
+// in place; otherwise, and for the last few entries, plain loads.  False if the copy's wait ran out.
+__device__ __forceinline__ bool stage_table(float* dst, const float* __restrict__ src, int n, int tid, int step,
+                                            uint64_t* bar) {
+  const int nb = (reinterpret_cast<uintptr_t>(src) & 15) == 0 ? (n & ~3) : 0;  // entries the bulk copy brings
+  if (nb > 0 && tid == 0) {
+    mbar_expect_tx(bar, (uint32_t)nb * 4u);
+    bulk_g2s(dst, src, (uint32_t)nb * 4u, bar);
+  }
+  for (int i0 = nb + tid; i0 < n; i0 += step * 8) {
     float v[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) v[k] = (i0 + k * step < n) ? __ldg(src + i0 + k * step) : 0.f;
@@ -71,6 +81,15 @@ __device__ __forceinline__ void stage_table(float* dst, const float* __restrict_
     for (int k = 0; k < 8; ++k)
       if (i0 + k * step < n) dst[i0 + k * step] = v[k] * kLog2e;
   }
+  if (nb > 0) {
+    if (!mbar_wait_bounded(bar, 0)) return false;
+    for (int i = tid * 4; i < nb; i += step * 4) {
+      float4 v = *reinterpret_cast<float4*>(dst + i);
+      v.x *= kLog2e; v.y *= kLog2e; v.z *= kLog2e; v.w *= kLog2e;
+      *reinterpret_cast<float4*>(dst + i) = v;
+    }
+  }
+  return true;
 }
 
 // Hardware barrier 1 over the first `n` threads of the CTA (the consumers): the producers do not

@@ -267,7 +267,9 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   uint64_t* empty = full + kMaxStages;                   // [kMaxStages] stage may be refilled
   uint64_t* gbar = empty + kMaxStages;                   // [kMaxGroups] group-internal barrier
   uint64_t* bbar = gbar + kMaxGroups;                    // phase B copies
+  uint64_t* tbar = reinterpret_cast<uint64_t*>(smem) + 30;  // bias table landed
   float* table_s = reinterpret_cast<float*>(smem + kBarBytes);
+  bool table_ok = true;
   unsigned char* stage0 = smem + kBarBytes + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
   const float* table_base = kTableSmem ? table_s : p.table;
   const int gsize = p.group_threads;
@@ -290,6 +292,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     }
     for (int g = 0; g < G; ++g) mbar_init(gbar + g, gwarps);
     mbar_init(bbar, 1);
+    mbar_init(tbar, 1);
     mbar_fence_init();
   }
   __syncthreads();
@@ -300,7 +303,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   const int n_items = p.header[SSW_H_PACKS];
   if constexpr (kTableSmem) {
     if (!is_producer) {  // the producers are already gathering the first items
-      stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons);
+      table_ok = stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons, tbar);
       consumer_sync(n_cons);
     }
   }
@@ -310,7 +313,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   // ------------------------------------------------------------------------------------------
   const int my_items =
       n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  bool timed_out = false;
+  bool timed_out = !table_ok;
   if (is_producer) {
     // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
     // of item i+3 (whose descriptor arrived an iteration ago) are requested while item i is issued,

@@ -246,7 +246,9 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   uint64_t* dempty = dfull + kMaxStages;                // phase 2: key stage may be refilled
   uint64_t* qfull = dempty + kMaxStages;                // phase 2: query tile landed
   uint64_t* qempty = qfull + 1;                         // phase 2: query stage may be refilled
+  uint64_t* tbar = reinterpret_cast<uint64_t*>(smem) + 30;  // bias table landed
   float* table_s = reinterpret_cast<float*>(smem + 256);
+  bool table_ok = true;
   unsigned char* stage0 = smem + 256 + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
   const float* table_base = kTableSmem ? table_s : p.table;
   const int gsize = kMmaGroupWarps * 32;
@@ -267,6 +269,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
     }
     mbar_init(qfull, PW);
     mbar_init(qempty, n_cons_warps);
+    mbar_init(tbar, 1);
     mbar_fence_init();
   }
   // unused row slots are read as keys/values (and masked): they must hold finite numbers
@@ -279,7 +282,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   const int n_items = p.header[SSW_H_PACKS];
   if constexpr (kTableSmem) {
     if (!is_producer) {  // the producers are already gathering the first items
-      stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons);
+      table_ok = stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons, tbar);
       consumer_sync(n_cons);
     }
   }
@@ -288,7 +291,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   // Phase 1: packs
   // ------------------------------------------------------------------------------------------
   const int my_items = n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  bool timed_out = false;
+  bool timed_out = !table_ok;
   if (is_producer) {
     // slot -> row of the pack: window wl = slot / cpad, i = slot % cpad, valid if wl < nwin && i < c.
     // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata

@@ -102,3 +102,46 @@ def test_skewed_one_million_bf16():
     coords, dims = scenes.skewed_scene(grid=126, window=9, p_dense=0.5, seed=0)
     st = _check_sampled(coords, dims, (9, 9, 9), (0, 0, 0), 6, 32, torch.bfloat16, BF16_TOL, n_sample=60, seed=31)
     assert st["c_max"] == 729 and st["voxels"] > 900_000
+
+
+def test_single_forward_20k_uniform_fp32():
+    """The CPU-runnable configuration as stated: 20 000 unique voxels uniform in a 128^3 grid
+    (seed 0), fp32 features ~N(0,1), C = 96, 3 heads x 32, window 7^3, no shift, Xavier-uniform qkv
+    weights (seed 1).  This size lies inside upstream's int32 index domain, so the oracle runs
+    upstream's whole operator chain; compared are the per-voxel output of the module and the COO
+    softmax values."""
+    from sparseswin3d_b200 import attention, window
+
+    dev = torch.device("cuda:0")
+    C, H, hd, W, grid, N = 96, 3, 32, (7, 7, 7), 128, 20_000
+    rng = np.random.default_rng(0)
+    flat = rng.choice(grid ** 3, size=N, replace=False)
+    z, y, x = np.unravel_index(flat, (grid, grid, grid))
+    coords = torch.from_numpy(np.stack([np.zeros_like(z), z, y, x], 1).astype(np.int32))
+    g = torch.Generator().manual_seed(0)
+    feats = torch.randn(N, C, generator=g)
+    torch.manual_seed(1)
+    m = attention.WindowAttentionSparse(C, H, W, qkv_bias=True)
+    torch.nn.init.xavier_uniform_(m.qkv.weight)
+    torch.nn.init.xavier_uniform_(m.proj.weight)
+    torch.nn.init.normal_(m.relative_position_bias_table, std=0.02)
+    idx, Bw, n, ws, ss, dp = O.window_keys(coords, 1, (grid,) * 3, W, (0, 0, 0))
+    assert Bw * H * n * hd < 2 ** 31
+    with torch.no_grad():
+        ref_out, ref_core, ref_attn = O.window_attention_forward(
+            feats, idx, Bw, n, H, m.qkv.weight, m.qkv.bias, m.proj.weight, m.proj.bias,
+            m.relative_position_bias_table, O.relative_position_index(W), None)
+        m = m.to(dev)
+        geom = window.resolve_geometry(1, (grid,) * 3, W, (0, 0, 0))
+        plan = window.bucket_windows(coords=coords.to(dev), geom=geom, **attention.plan_params(H, hd, torch.float32, W))
+        qkv = m.qkv(feats.to(dev)).reshape(N, 3, H, hd)
+        core, attn = attention.window_attention_fused(qkv, plan, m.relative_position_bias_table, m.scale,
+                                                      use_mask=False, return_attn=True)
+        out = m.proj(core)
+    assert plan.stats()["error"] == 0
+    # the Linear layers run in cuBLAS on the device and in the CPU BLAS for the oracle: their own
+    # rounding differences (1e-6) pass through the attention
+    assert rel_err(core.cpu(), ref_core) <= 2e-5
+    assert rel_err(out.cpu(), ref_out) <= 2e-5
+    assert attn.numel() == ref_attn.values.numel()
+    assert rel_err(attn.cpu(), ref_attn.values) <= 2e-5
