@@ -566,9 +566,14 @@ static MmaShape mma_shape(int tile, int heads, int head_dim, const int32_t rpb_w
   s.row_stride = 3 * C * 2 + 16;  // +16 B: per-row metadata, and consecutive rows fall on different banks
   s.stage_bytes = kMmaStageRowsOff + tile * s.row_stride;
   const int tf = (2 * rpb_window[0] - 1) * (2 * rpb_window[1] - 1) * (2 * rpb_window[2] - 1) * heads;
-  s.table_floats = tf * 4 <= 40 * 1024 ? tf : 0;
-  const size_t fixed = 256 + ((s.table_floats * 4 + 15) & ~15);
-  int stages = (int)((size_t(226) * 1024 - fixed) / s.stage_bytes);
+  // The bias table goes to shared memory when four stages still fit beside it (look-ups from global
+  // memory cost a dense window about a quarter of its time); otherwise it stays in global memory.
+  const size_t budget = size_t(226) * 1024;
+  const size_t tbytes = ((size_t)tf * 4 + 15) & ~size_t(15);
+  const bool table_smem = 256 + tbytes + 4 * (size_t)s.stage_bytes <= budget;
+  s.table_floats = table_smem ? tf : 0;
+  const size_t fixed = 256 + (table_smem ? tbytes : 0);
+  int stages = (int)((budget - fixed) / s.stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
   int groups = stages - 1;
   if (groups > kMaxGroups) groups = kMaxGroups;
