@@ -191,6 +191,22 @@ int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t head_dim,
                    const float* table, const int32_t rpb_window[3], float scale, int use_mask,
                    void* out, void* attn_vals, void* stream);
 
+/* Backward of ssw_attn_fused: gradients of qkv and of the bias table from the gradient of `out`,
+ * with the probabilities recomputed instead of stored.  It replaces what upstream's autograd runs
+ * for the same span: softmax_last_dim_backward (ops.cu:169-194, swin3d_base.py:177-188) and the
+ * blocked gradient products rc_cr / rr_rc / cr_rr with their transposes (ops.cu:422-557, 663-715,
+ * 945-1031; swin3d_base.py:106-138), the index_select gradients of sp_add_rpb (:557-566) and the
+ * un-sort (:674-675).
+ *   grad_out [N, heads*head_dim] and dqkv [N, 3, heads, head_dim] of `dtype`, voxel order
+ *   dtable   [(2Wz-1)(2Wy-1)(2Wx-1), heads] fp32: the gradient is ADDED to it (zero it first)
+ *   workspace: ssw_attn_fused_bwd_workspace_floats(N, heads) floats, 16-byte aligned
+ * Works on contiguous and padded plans alike. */
+int64_t ssw_attn_fused_bwd_workspace_floats(int64_t n_vox, int32_t heads);
+int ssw_attn_fused_bwd(const void* qkv, const void* grad_out, int dtype, int32_t heads, int32_t head_dim,
+                       const ssw_plan_layout* L, const int32_t* plan,
+                       const float* table, const int32_t rpb_window[3], float scale, int use_mask,
+                       void* dqkv, float* dtable, float* workspace, void* stream);
+
 /* ---- COO operator surface ----------------------------------------------------------
  * The unfused operators upstream exports from sparse_swin/ops.cpp:7-18, with upstream's layouts.
  * Functions whose output size depends on the data come in two steps: a *_plan call that leaves

@@ -12,6 +12,48 @@ from ._lib import check, dtype_code, lib, ptr, stream_ptr
 from .window import WindowPlan, bucket_windows
 
 
+def window_attention_fused_backward(qkv: torch.Tensor, grad_out: torch.Tensor, plan: WindowPlan, table: torch.Tensor,
+                                    scale: float, use_mask: bool = False):
+    """Gradients of `window_attention_fused` with respect to qkv and the bias table, given the
+    gradient of its output (probabilities are recomputed, nothing of the forward is kept).
+    Returns (dqkv [N,3,H,hd] in qkv's dtype, dtable fp32 in the table's shape)."""
+    if not (qkv.is_cuda and qkv.is_contiguous() and qkv.dim() == 4 and qkv.shape[1] == 3):
+        raise _lib.SswError("qkv must be a contiguous CUDA tensor [N, 3, heads, head_dim]")
+    N, _, H, hd = qkv.shape
+    if N != plan.layout.n_vox:
+        raise _lib.SswError(f"plan was built for {plan.layout.n_vox} voxels, qkv has {N}")
+    grad_out = grad_out.to(qkv.dtype).contiguous()
+    if grad_out.shape != (N, H * hd):
+        raise _lib.SswError("grad_out must be [N, heads*head_dim]")
+    tab = table.detach()
+    if tab.dtype != torch.float32 or not tab.is_contiguous():
+        tab = tab.float().contiguous()
+    dqkv = torch.empty_like(qkv)
+    dtable = torch.zeros_like(tab)
+    ws = torch.empty(max(int(lib.ssw_attn_fused_bwd_workspace_floats(N, H)), 4), dtype=torch.float32, device=qkv.device)
+    rwc = (_lib.i32 * 3)(*plan.rpb_window)
+    check(lib.ssw_attn_fused_bwd(ptr(qkv), ptr(grad_out), dtype_code(qkv.dtype), H, hd, plan.layout, ptr(plan.plan),
+                                 ptr(tab), rwc, float(scale), int(bool(use_mask)), ptr(dqkv), ptr(dtable), ptr(ws),
+                                 stream_ptr(qkv.device)), "ssw_attn_fused_bwd")
+    return dqkv, dtable
+
+
+class FusedWindowAttention(torch.autograd.Function):
+    """window_attention_fused with autograd: forward keeps qkv and the table, backward recomputes."""
+
+    @staticmethod
+    def forward(ctx, qkv, table, plan, scale, use_mask):
+        ctx.plan, ctx.scale, ctx.use_mask = plan, float(scale), bool(use_mask)
+        ctx.save_for_backward(qkv, table)
+        return window_attention_fused(qkv, plan, table, scale, use_mask=use_mask)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        qkv, table = ctx.saved_tensors
+        dqkv, dtable = window_attention_fused_backward(qkv, grad_out, ctx.plan, table, ctx.scale, ctx.use_mask)
+        return dqkv, dtable.to(table.dtype), None, None, None
+
+
 def default_tile_rows(num_heads: int, head_dim: int, dtype: torch.dtype, rpb_window: Sequence[int] = (7, 7, 7)) -> int:
     """Rows per work item the fused kernel wants for this configuration (pass it to bucket_windows)."""
     rw = (_lib.i32 * 3)(*[int(x) for x in rpb_window])
@@ -81,7 +123,7 @@ class WindowAttentionSparse(nn.Module):
     unchanged.  ``forward(x, mask)`` accepts what upstream's forward accepts: an object with
     ``features`` [N,C], ``indices`` [N,2] int32 (window, pos), ``batch_size`` (all windows, empty
     ones included), ``spatial_shape`` (n,) and ``replace_feature`` (swin3d_base.py:654-677).
-    Inference only: the fused kernel has no autograd."""
+    Differentiable: with autograd recording the fused forward is paired with a fused backward."""
 
     def __init__(self, dim: int, num_heads: int, window_size: Sequence[int], qkv_bias: bool = False,
                  attn_drop: float = 0.0, proj_drop: float = 0.0) -> None:
@@ -117,10 +159,12 @@ class WindowAttentionSparse(nn.Module):
                               mask=mask, **plan_params(self.num_heads, self.dim // self.num_heads, dtype,
                                                        self.window_size))
 
-    @torch.no_grad()
     def forward_features(self, features: torch.Tensor, plan: WindowPlan, use_mask: bool) -> torch.Tensor:
         qkv = self.qkv(features).reshape(-1, 3, self.num_heads, self.dim // self.num_heads)
-        core = window_attention_fused(qkv, plan, self.relative_position_bias_table, self.scale, use_mask)
+        if torch.is_grad_enabled() and (qkv.requires_grad or self.relative_position_bias_table.requires_grad):
+            core = FusedWindowAttention.apply(qkv.contiguous(), self.relative_position_bias_table, plan, self.scale, use_mask)
+        else:
+            core = window_attention_fused(qkv, plan, self.relative_position_bias_table, self.scale, use_mask)
         return self.proj_drop(self.proj(core))
 
     def forward_unfused(self, x, mask):
@@ -148,12 +192,13 @@ class WindowAttentionSparse(nn.Module):
         return x.replace_feature(self.proj_drop(self.proj(x.features)))
 
     def forward(self, x, mask, plan: Optional[WindowPlan] = None, fused: Optional[bool] = None):
-        """fused=None picks the fused kernel unless autograd is recording (it has no backward)."""
+        """The fused kernels by default (differentiable: the backward recomputes the probabilities);
+        fused=False runs upstream's operator chain on the COO surface instead."""
         if fused is None:
-            fused = not (torch.is_grad_enabled() and (x.features.requires_grad or self.qkv.weight.requires_grad))
+            fused = True
         if not fused:
             return self.forward_unfused(x, mask)
-        with torch.no_grad():
-            if plan is None:
+        if plan is None:
+            with torch.no_grad():
                 plan = self.plan(x, mask, x.features.dtype)
-            return x.replace_feature(self.forward_features(x.features, plan, mask is not None))
+        return x.replace_feature(self.forward_features(x.features, plan, mask is not None))

@@ -280,7 +280,6 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   const int row_elems = 3 * C;  // q|k|v elements staged per voxel
   const uint32_t copy_bytes = row_elems * sizeof(T);
   const int copy_off = kHalf ? row_elems * 2 : 0;  // 16-bit rows land in the upper half of the fp32 row
-  const uint32_t out_bytes = C * sizeof(T);
   const int n_hiter = H / p.HG;
   const int data_bytes = row_elems * 4;      // fp32 payload of a staged row; its metadata follows
   const float qscale = p.scale * kLog2e;     // scores are kept in the log2 domain
