@@ -40,3 +40,32 @@ def rel_err(x: torch.Tensor, ref: torch.Tensor) -> float:
     x = x.double()
     rms = ref.pow(2).mean().sqrt().clamp_min(1e-30)
     return float(((x - ref).abs() / torch.maximum(ref.abs(), rms)).max()) if ref.numel() else 0.0
+
+
+def digest_i64(a) -> int:
+    """Order-sensitive checksum of an integer array (wraps in int64, deterministically)."""
+    import numpy as np
+
+    a = np.asarray(a).reshape(-1).astype(np.int64)
+    w = (np.arange(a.size, dtype=np.int64) % 1000003) + 1
+    with np.errstate(over="ignore"):
+        return int((a * w).sum() & np.int64(2 ** 62 - 1))
+
+
+def room_crop_case(shift=(0, 0, 0), crop=200, heads=3, head_dim=32, window=(7, 7, 7), seed=0):
+    """The x,y < crop corner of the benchmark's 150 000-voxel room (about 36 000 voxels): large and
+    surface-sparse like the benchmark scene, and still inside upstream's int32 index domain."""
+    import numpy as np
+
+    coords, dims = scenes.room_scene(150_000, seed=seed)
+    keep = (coords[:, 1] < crop) & (coords[:, 2] < crop)
+    coords = torch.from_numpy(coords[keep].copy())
+    dims = (crop, crop, dims[2])
+    idx, Bw, n, ws, ss, dp = O.window_keys(coords, 1, dims, window, shift)
+    g = torch.Generator().manual_seed(1000 + seed)
+    qkv = torch.randn(coords.shape[0], 3, heads, head_dim, generator=g)
+    table = torch.randn((2 * window[0] - 1) ** 3, heads, generator=g) * 0.5
+    mask = O.compute_mask(dp, ws, ss) if any(s > 0 for s in ss) else None
+    return dict(coords=coords, dims=dims, batch=1, window=window, shift=shift, indices=idx, n_windows=Bw, n=n, ws=ws,
+                ss=ss, dims_p=dp, qkv=qkv, table=table, rpi=O.relative_position_index(window), mask=mask, heads=heads,
+                head_dim=head_dim, scale=head_dim ** -0.5)

@@ -19,7 +19,39 @@ ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 
 from oracle.build_ref import load_ref  # noqa: E402
-from tests.cases import make_case  # noqa: E402
+from tests.cases import digest_i64, make_case, room_crop_case  # noqa: E402
+
+# Larger cases are stored as digests: checksums of every index array, sums of every value array and
+# a fixed sample of output rows and softmax values (inputs are regenerated from their seeds).
+DIGEST_CASES = {
+    "room_crop_wmsa": dict(shift=(0, 0, 0)),
+    "room_crop_swmsa": dict(shift=(3, 3, 3)),
+}
+INT_KEYS = ("idx_qv", "perm_qv", "idx_k", "perm_k", "qk_idx", "c", "softmax_rows", "pv_idx", "c_pv", "permute_order",
+            "arg_sort")
+VAL_KEYS = ("qk_val", "pre_softmax", "softmax", "pv_val", "out")
+N_SAMPLE = 512
+
+
+def digest_of(res):
+    rng = np.random.default_rng(5)
+    d = {}
+    for k in INT_KEYS:
+        d["crc_" + k] = np.array(digest_i64(res[k]), dtype=np.int64)
+        d["len_" + k] = np.array(res[k].size, dtype=np.int64)
+    for k in VAL_KEYS:
+        v = res[k].astype(np.float64)
+        d["sum_" + k] = np.array(v.sum())
+        d["abs_" + k] = np.array(np.abs(v).sum())
+    rows = np.sort(rng.choice(res["out"].shape[0], size=N_SAMPLE, replace=False))
+    d["sample_rows"] = rows.astype(np.int64)
+    d["sample_out"] = res["out"][rows]
+    pos = np.sort(rng.choice(res["softmax"].size, size=8 * N_SAMPLE, replace=False))
+    d["sample_pos"] = pos.astype(np.int64)
+    d["sample_softmax"] = res["softmax"][pos]
+    d["sample_qk_idx"] = res["qk_idx"][:, pos]
+    return d
+
 
 CASES = {
     "wmsa_h3_hd32": dict(n_vox=100, grid=16, heads=3, head_dim=32, shift=(0, 0, 0), seed=11),
@@ -108,6 +140,14 @@ def main():
                    in_mask=case["mask"].numpy() if case["mask"] is not None else np.zeros((0, 0), np.int8))
         np.savez_compressed(outdir / f"{name}.npz", **res)
         print(name, {k: v.shape for k, v in res.items() if k in ("qk_val", "out", "perm_qv")})
+    for name, kw in DIGEST_CASES.items():
+        case = room_crop_case(**kw)
+        assert case["n_windows"] * case["heads"] * case["n"] * case["head_dim"] < 2 ** 31  # upstream's index domain
+        res = run_case(ref, case, dev)
+        d = digest_of(res)
+        d.update(in_n_vox=np.array(case["coords"].shape[0]), in_shift=np.array(case["shift"]))
+        np.savez_compressed(outdir / f"digest_{name}.npz", **d)
+        print(name, case["coords"].shape[0], "voxels", res["qk_val"].size, "scores")
 
 
 if __name__ == "__main__":

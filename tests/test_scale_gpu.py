@@ -145,3 +145,58 @@ def test_single_forward_20k_uniform_fp32():
     assert rel_err(out.cpu(), ref_out) <= 2e-5
     assert attn.numel() == ref_attn.values.numel()
     assert rel_err(attn.cpu(), ref_attn.values) <= 2e-5
+
+
+DIGESTS = sorted((__import__("pathlib").Path(__file__).parent / "golden").glob("digest_*.npz"))
+
+
+@pytest.mark.parametrize("path", DIGESTS, ids=[p.stem for p in DIGESTS])
+def test_room_crop_against_upstream_digest(path):
+    """The CUDA path against the unmodified upstream extension on the x,y<200 corner of the benchmark
+    room (35 935 voxels, 1.2 M scores), through the stored digest: the operator chain's index arrays
+    by checksum (bit exact), its value arrays by their sums, the fused kernel's output and COO
+    softmax values on the sampled rows / positions."""
+    from sparseswin3d_b200 import attention, ops, window
+    from tests.cases import digest_i64, room_crop_case
+
+    dev = torch.device("cuda:0")
+    d = dict(np.load(path))
+    case = room_crop_case(shift=tuple(d["in_shift"].tolist()))
+    idx, qkv = case["indices"].to(dev), case["qkv"].to(dev)
+    Bw, n, H, hd = case["n_windows"], case["n"], case["heads"], case["head_dim"]
+
+    def same(a, key):
+        assert a.dtype == torch.int32 and a.numel() == int(d["len_" + key]), key
+        assert digest_i64(a.cpu().numpy()) == int(d["crc_" + key]), key
+
+    def sums(x, key):
+        x = x.double()
+        assert abs(float(x.abs().sum()) - float(d["abs_" + key])) <= 1e-5 * float(d["abs_" + key]), key
+        assert abs(float(x.sum()) - float(d["sum_" + key])) <= 1e-5 * float(d["abs_" + key]), key
+
+    # operator chain
+    iqv, pqv, ik, pk = ops.qkv_sparse_indices(idx, Bw, n, H, hd)
+    for a, k in ((iqv, "idx_qv"), (pqv, "perm_qv"), (ik, "idx_k"), (pk, "perm_k")):
+        same(a, k)
+    iq, ikk = iqv.index_select(1, pqv), ik.index_select(1, pk)
+    q_v = qkv[:, 0].reshape(-1).index_select(0, pqv) * case["scale"]
+    k_v = qkv[:, 1].reshape(-1).index_select(0, pk)
+    v_v = qkv[:, 2].reshape(-1).index_select(0, pqv)
+    a_idx, a_val, a_shape, c = ops.matmul_cuda_naive(q_v, iq, [Bw, H, n, hd], k_v, ikk, [Bw, H, hd, n], "q_k")
+    same(a_idx, "qk_idx"), same(c, "c"), sums(a_val, "qk_val")
+    arg_sort, _ = ops.return_inverse(ops.flatten_indices(idx.T.contiguous(), [Bw, n]), -1)
+    same(arg_sort, "arg_sort")
+
+    # fused kernel
+    geom = window.resolve_geometry(1, case["dims"], case["window"], case["shift"])
+    plan = window.bucket_windows(coords=case["coords"].to(dev), geom=geom, **attention.plan_params(H, hd, torch.float32))
+    out, attn = attention.window_attention_fused(qkv, plan, case["table"].to(dev), case["scale"],
+                                                 use_mask=case["mask"] is not None, return_attn=True)
+    assert plan.stats()["error"] == 0
+    assert torch.equal(plan.inv_perm, arg_sort)
+    sums(out, "out"), sums(attn, "softmax")
+    rows = torch.from_numpy(d["sample_rows"]).to(dev)
+    assert rel_err(out[rows].cpu(), torch.from_numpy(d["sample_out"])) <= FP32_TOL
+    pos = torch.from_numpy(d["sample_pos"]).to(dev)
+    assert torch.equal(a_idx[:, pos].cpu(), torch.from_numpy(d["sample_qk_idx"]))
+    assert rel_err(attn[pos].cpu(), torch.from_numpy(d["sample_softmax"])) <= FP32_TOL
