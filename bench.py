@@ -475,6 +475,46 @@ def cpu_baseline(seconds: float = 15.0):
                       "oracle/ssw_oracle.py on torch CPU"}
 
 
+def _upstream_on_gpu(O, c, dims, qkv, table, rpi, reps: int = 5):
+    """Extra information beside the CPU number: upstream's own CUDA extension (built unmodified into
+    oracle/_ref/ where the upstream sources were available), driven through the same two passes on
+    the same sample, on cuda:0.  None when there is no GPU or no such build."""
+    try:
+        if not torch.cuda.is_available():
+            return None
+        from oracle import upstream_chain
+        from oracle.build_ref import load_ref
+
+        ref = load_ref()
+        if ref is None:
+            return None
+        dev = torch.device("cuda:0")
+        passes = []
+        for shift in ((0, 0, 0), SHIFT):
+            idx, Bw, n, ws, ss, dp = O.window_keys(c, 1, dims, WINDOW, shift)
+            mask = O.compute_mask(dp, ws, ss).to(dev) if any(ss) else None
+            passes.append((idx.to(dev), Bw, n, mask))
+        qkv_d, table_d, rpi_d = qkv.to(dev), table.to(dev), rpi.to(dev)
+
+        def step():
+            for idx, Bw, n, mask in passes:
+                upstream_chain.forward(ref, idx, qkv_d, Bw, n, HEAD_DIM ** -0.5, table_d, rpi_d, mask)
+
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            step()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": 2.0 * c.shape[0] / dt, "unit": UNIT, "ms_per_step": dt * 1e3,
+                "sample": f"upstream ops.cu, unmodified, on cuda:0: W-MSA+SW-MSA attention core (qkv given, window "
+                          f"indices and mask given) on the same {c.shape[0]}-voxel sample, wall clock over {reps} steps"}
+    except Exception as e:  # informational only
+        return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
@@ -495,6 +535,7 @@ def run_reference(args):
     v = 2.0 * c.shape[0] * steps / dt
     sample = (f"each step = W-MSA+SW-MSA on the x,y<200 corner of the scene ({c.shape[0]} voxels, fp32); upstream has no "
               "CPU path and its CUDA extension needs a GPU, so this is oracle/ssw_oracle.py (a PyTorch CPU restatement)")
+    upstream_gpu = _upstream_on_gpu(O, c, dims, qkv, table, rpi)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -503,6 +544,7 @@ def run_reference(args):
                                "window 7^3", "voxels_per_step": 2 * c.shape[0]},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "upstream_gpu": upstream_gpu,
     }), flush=True)
 
 
