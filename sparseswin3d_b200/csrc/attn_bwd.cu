@@ -13,9 +13,10 @@
 //
 // Two kernels over the plan's work items, one thread per (row, head), rows read straight from
 // global memory (the rows of a window are re-read by its own threads only, so they stay in L1/L2):
-//   k_attn_bwd_q : per query row two sweeps over the window's keys (row statistics, then dq and
-//                  the bias gradient); leaves (m_i, 1/(l_i+1e-8), D_i) per (row, head) for
-//   k_attn_bwd_kv: per key row one sweep over the window's queries -> dk, dv.
+//   k_attn_bwd_q : per query row one sweep over the window's keys with an online maximum: the row
+//                  statistics and dq (as (A - D B)/(l+1e-8) with A = sum e dP k, B = sum e k);
+//                  leaves (m_i, 1/(l_i+1e-8), D_i) per (row, head) for
+//   k_attn_bwd_kv: per key row one sweep over the window's queries -> dk, dv and the bias gradient.
 // No atomics on the row gradients; the bias gradient is accumulated in a shared-memory copy of the
 // table per CTA (when it fits) and flushed with global atomics.
 #include <math.h>
@@ -124,10 +125,7 @@ __device__ __forceinline__ float score2(float qk, float qs, const float* table, 
 
 template <typename T, int HD>
 __global__ void __launch_bounds__(128) k_attn_bwd_q(BwdParams p) {
-  extern __shared__ float dtab_s[];
   const int H = p.H, C = p.C;
-  for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) dtab_s[i] = 0.f;
-  __syncthreads();
   const int n_items = p.header[SSW_H_PACKS];
   const float qs = p.scale * kLog2e;
   const T* qkv = reinterpret_cast<const T*>(p.qkv);
@@ -143,8 +141,13 @@ __global__ void __launch_bounds__(128) k_attn_bwd_q(BwdParams p) {
       float q[HD], go[HD];
       load_row<T, HD>(qkv + (int64_t)vi * 3 * C + h * HD, q);
       load_row<T, HD>(reinterpret_cast<const T*>(p.grad_out) + (int64_t)vi * C + h * HD, go);
-      // sweep 1: row maximum (from 0), denominator, and sum_j e_ij dP_ij
+      // One sweep over the window's keys with the running maximum (from 0): denominator l,
+      // dn = sum_j e_ij dP_ij, A = sum_j e_ij dP_ij k_j and B = sum_j e_ij k_j, from which
+      // D = dn / (l + 1e-8) and dq = (A - D B) / (l + 1e-8).
       float m = 0.f, l = 0.f, dn = 0.f;
+      float dq[HD], kb[HD];
+#pragma unroll
+      for (int e = 0; e < HD; ++e) dq[e] = kb[e] = 0.f;
       for (int j = 0; j < c; ++j) {
         const int vj = __ldg(p.pack_perm + first + j), mj = __ldg(p.pack_meta + first + j);
         float k[HD], v[HD];
@@ -156,48 +159,36 @@ __global__ void __launch_bounds__(128) k_attn_bwd_q(BwdParams p) {
           const float corr = fast_exp2(m - s2);
           l *= corr;
           dn *= corr;
+#pragma unroll
+          for (int e = 0; e < HD; ++e) { dq[e] *= corr; kb[e] *= corr; }
           m = s2;
         }
-        const float e = fast_exp2(s2 - m);
-        l += e;
-        dn = fmaf(e, dp, dn);
+        const float ex = fast_exp2(s2 - m);
+        const float edp = ex * dp;
+        l += ex;
+        dn += edp;
+#pragma unroll
+        for (int e = 0; e < HD; ++e) {
+          dq[e] = fmaf(edp, k[e], dq[e]);
+          kb[e] = fmaf(ex, k[e], kb[e]);
+        }
       }
       const float inv = 1.0f / (l + 1e-8f);
       const float D = dn * inv;
       reinterpret_cast<float4*>(p.stats)[(int64_t)row * H + h] = make_float4(m, inv, D, 0.f);
-      // sweep 2: dS_ij -> dq_i and the bias gradient
-      float dq[HD];
 #pragma unroll
-      for (int e = 0; e < HD; ++e) dq[e] = 0.f;
-      for (int j = 0; j < c; ++j) {
-        const int vj = __ldg(p.pack_perm + first + j), mj = __ldg(p.pack_meta + first + j);
-        float k[HD], v[HD];
-        load_row<T, HD>(qkv + (int64_t)vj * 3 * C + C + h * HD, k);
-        load_row<T, HD>(qkv + (int64_t)vj * 3 * C + 2 * C + h * HD, v);
-        const float s2 = score2(dot<HD>(q, k), qs, p.table, rel_i_off, mi, mj, H, h, p.use_mask != 0);
-        const float pij = fast_exp2(s2 - m) * inv;
-        const float ds = pij * (dot<HD>(go, v) - D);
-#pragma unroll
-        for (int e = 0; e < HD; ++e) dq[e] = fmaf(ds, k[e], dq[e]);
-        const int ti = (rel_i_off - meta_rel(mj)) * H + h;
-        if (p.table_floats > 0) atomicAdd(dtab_s + ti, ds);
-        else atomicAdd(p.dtable + ti, ds);
-      }
+      for (int e = 0; e < HD; ++e) dq[e] = (dq[e] - D * kb[e]) * inv;
       store_row<T, HD>(reinterpret_cast<T*>(p.dqkv) + (int64_t)vi * 3 * C + h * HD, dq, p.scale);
-    }
-  }
-  if (p.table_floats > 0) {
-    __syncthreads();
-    for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) {
-      const float g = dtab_s[i];
-      if (g != 0.f) atomicAdd(p.dtable + i, g);
     }
   }
 }
 
 template <typename T, int HD>
 __global__ void __launch_bounds__(128) k_attn_bwd_kv(BwdParams p) {
+  extern __shared__ float dtab_s[];
   const int H = p.H, C = p.C;
+  for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) dtab_s[i] = 0.f;
+  __syncthreads();
   grid_dependency_wait();  // the row statistics come from the kernel this one is chained behind
   const int n_items = p.header[SSW_H_PACKS];
   const float qs = p.scale * kLog2e;
@@ -229,10 +220,20 @@ __global__ void __launch_bounds__(128) k_attn_bwd_kv(BwdParams p) {
           dk[e] = fmaf(ds, q[e], dk[e]);
           dv[e] = fmaf(pij, go[e], dv[e]);
         }
+        const int ti = (meta_rel(mi) + p.rel_off - meta_rel(mj)) * H + h;
+        if (p.table_floats > 0) atomicAdd(dtab_s + ti, ds);
+        else atomicAdd(p.dtable + ti, ds);
       }
       T* dst = reinterpret_cast<T*>(p.dqkv) + (int64_t)vj * 3 * C + h * HD;
       store_row<T, HD>(dst + C, dk, p.scale);
       store_row<T, HD>(dst + 2 * C, dv, 1.0f);
+    }
+  }
+  if (p.table_floats > 0) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) {
+      const float g = dtab_s[i];
+      if (g != 0.f) atomicAdd(p.dtable + i, g);
     }
   }
 }
@@ -243,11 +244,11 @@ static int launch_bwd(const BwdParams& p, cudaStream_t stream) {
   SSW_CUDA_TRY(cudaGetDevice(&dev));
   SSW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const size_t smem = (size_t)p.table_floats * 4;
-  auto kq = k_attn_bwd_q<T, HD>;
-  if (smem > 48 * 1024) SSW_CUDA_TRY(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kq<<<sms * 8, 128, smem, stream>>>(p);
+  auto kkv = k_attn_bwd_kv<T, HD>;
+  if (smem > 48 * 1024) SSW_CUDA_TRY(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  k_attn_bwd_q<T, HD><<<sms * 8, 128, 0, stream>>>(p);
   SSW_LAUNCH_CHECK("k_attn_bwd_q");
-  SSW_CUDA_TRY(launch_chained(k_attn_bwd_kv<T, HD>, dim3(sms * 8), dim3(128), 0, stream, p));
+  SSW_CUDA_TRY(launch_chained(kkv, dim3(sms * 8), dim3(128), smem, stream, p));
   return SSW_OK;
 }
 

@@ -163,3 +163,24 @@ def test_skewed_occupancy_window9(dtype, tol):
     counts = np.unique(idx[:, 0].numpy(), return_counts=True)[1]
     assert st["sum_c2"] == int((counts.astype(np.int64) ** 2).sum())
     assert rel_err(out.float().cpu(), ref) <= tol
+
+
+def test_plan_buffer_and_scratch_are_reused():
+    """A caller that builds plans repeatedly passes its own scratch and plan buffers: the plan then
+    lives in the caller's buffer and equals a freshly allocated one."""
+    from sparseswin3d_b200 import attention, window
+
+    dev = torch.device("cuda:0")
+    case = make_case(n_vox=2000, grid=30, shift=(3, 3, 3), seed=9)
+    g = window.resolve_geometry(1, case["dims"], case["window"], case["shift"])
+    pp = attention.plan_params(3, 32, torch.float32)
+    ref = window.bucket_windows(coords=case["coords"].to(dev), geom=g, **pp)
+    buf = torch.empty(ref.layout.plan_ints + 100, dtype=torch.int32, device=dev)
+    scratch = torch.empty(ref.layout.scratch_ints, dtype=torch.int32, device=dev)
+    for _ in range(2):
+        plan = window.bucket_windows(coords=case["coords"].to(dev), geom=g, scratch=scratch, plan_buffer=buf, **pp)
+        assert plan.plan.data_ptr() == buf.data_ptr()
+        assert torch.equal(plan.perm, ref.perm) and torch.equal(plan.inv_perm, ref.inv_perm)
+        a = attention.window_attention_fused(case["qkv"].to(dev), plan, case["table"].to(dev), case["scale"], use_mask=True)
+        b = attention.window_attention_fused(case["qkv"].to(dev), ref, case["table"].to(dev), case["scale"], use_mask=True)
+        assert torch.equal(a, b)
