@@ -30,6 +30,7 @@ struct AttnParams {
   int group_threads;  // threads of one consumer group (multiple of 32) = ceil32(tile * HG)
   int groups, stages;
   int prod_warps;     // warps that issue the row copies of an item
+  int split;          // CUDA-core kernel: a (row, head) is shared by two lanes, half the channels each
   float scale;
   int use_mask;
   int row_stride;     // bytes between fp32 rows in a stage

@@ -233,6 +233,84 @@ __device__ __forceinline__ void attend_keys_m(bool use_mask, RowState<HD>& st, c
                                                  table_h, my_region, inv_l, emit_dst);
 }
 
+// Channel-split form: two adjacent lanes share one (query row, head), each holding half of the
+// head's channels (q, K/V slices, accumulators).  The partial dot products are combined with one
+// shuffle per key.  Same shared-memory traffic as the one-thread form, twice the warps to hide the
+// dependent max / exp / accumulate chain behind.
+template <int HH, int N, bool kTableSmem, bool kMask>
+__device__ __forceinline__ void attend_chunk_split(RowState<HH>& st, const unsigned char* kp, int row_stride, int meta_off,
+                                                   int v_off, const unsigned char* table_h, int my_region,
+                                                   unsigned lanes) {
+  const float mask_add = -100.0f * kLog2e;
+  float s[N];
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    const float4* kr = reinterpret_cast<const float4*>(kp + u * row_stride);
+    float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int e = 0; e < HH / 4; ++e) {
+      const float4 kv = kr[e];
+      sa = __ffma2_rn(st.q[2 * e], make_float2(kv.x, kv.y), sa);
+      sb = __ffma2_rn(st.q[2 * e + 1], make_float2(kv.z, kv.w), sb);
+    }
+    s[u] = (sa.x + sb.x) + (sa.y + sb.y);
+  }
+#pragma unroll
+  for (int u = 0; u < N; ++u) s[u] += __shfl_xor_sync(lanes, s[u], 1);
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    const int2 km = *reinterpret_cast<const int2*>(kp + u * row_stride + meta_off);
+    const float bias = kTableSmem ? *reinterpret_cast<const float*>(table_h - km.x)
+                                  : __ldg(reinterpret_cast<const float*>(table_h - km.x)) * kLog2e;
+    s[u] += bias;
+    if (kMask && my_region != (km.y & 31)) s[u] += mask_add;
+  }
+  float mc = s[0];
+#pragma unroll
+  for (int u = 1; u < N; ++u) mc = fmaxf(mc, s[u]);
+  if (mc > st.m) {
+    const float corr = fast_exp2(st.m - mc);
+    st.l *= corr;
+    const float2 c2 = make_float2(corr, corr);
+#pragma unroll
+    for (int e = 0; e < HH / 2; ++e) st.acc[e] = __fmul2_rn(st.acc[e], c2);
+    st.m = mc;
+  }
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    const float pu = fast_exp2(s[u] - st.m);
+    st.l += pu;
+    const float2 p2 = make_float2(pu, pu);
+    const float4* vr = reinterpret_cast<const float4*>(kp + u * row_stride + v_off);
+#pragma unroll
+    for (int e = 0; e < HH / 4; ++e) {
+      const float4 vv = vr[e];
+      st.acc[2 * e] = __ffma2_rn(p2, make_float2(vv.x, vv.y), st.acc[2 * e]);
+      st.acc[2 * e + 1] = __ffma2_rn(p2, make_float2(vv.z, vv.w), st.acc[2 * e + 1]);
+    }
+  }
+}
+
+// k_off: byte offset of this lane's half of the head's k slice; meta_off is taken from there
+template <int HH, bool kTableSmem, bool kMask>
+__device__ __forceinline__ void attend_keys_split(RowState<HH>& st, const unsigned char* rows, int row_stride,
+                                                  int data_bytes, int first_row, int n_keys, int k_off, int C,
+                                                  const float* table_h, int my_region, unsigned lanes) {
+  const unsigned char* kp = rows + (size_t)first_row * row_stride + k_off;
+  const int meta_off = data_bytes - k_off;
+  const int v_off = C * 4;
+  const unsigned char* tab = reinterpret_cast<const unsigned char*>(table_h);
+  int j = 0;
+  for (; j + 4 <= n_keys; j += 4, kp += 4 * row_stride)
+    attend_chunk_split<HH, 4, kTableSmem, kMask>(st, kp, row_stride, meta_off, v_off, tab, my_region, lanes);
+  switch (n_keys - j) {
+    case 1: attend_chunk_split<HH, 1, kTableSmem, kMask>(st, kp, row_stride, meta_off, v_off, tab, my_region, lanes); break;
+    case 2: attend_chunk_split<HH, 2, kTableSmem, kMask>(st, kp, row_stride, meta_off, v_off, tab, my_region, lanes); break;
+    case 3: attend_chunk_split<HH, 3, kTableSmem, kMask>(st, kp, row_stride, meta_off, v_off, tab, my_region, lanes); break;
+    default: break;
+  }
+}
+
 // acc * inv_l as T, 16-byte vector stores (global or shared destination)
 template <typename T, int HD>
 __device__ __forceinline__ void store_out(T* dst, const RowState<HD>& st, float inv_l) {
@@ -257,7 +335,7 @@ __device__ __forceinline__ void store_out(T* dst, const RowState<HD>& st, float 
   }
 }
 
-template <typename T, int HD, bool kTableSmem, int MAXT>
+template <typename T, int HD, bool kTableSmem, int MAXT, bool kSplit>
 __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr bool kHalf = sizeof(T) == 2;
@@ -424,6 +502,37 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
           break;
         }
       }
+      if constexpr (kSplit) {
+        // lanes 2t, 2t+1 share (row, head): lane parity picks the half of the head's channels
+        constexpr int HH = HD / 2;
+        const int x = ltid & 1, rh = ltid >> 1;
+        const int hgs = rh / tile, rs = rh - hgs * tile;
+        if (hgs < p.HG && rs < q_rows) {
+          const unsigned lanes = __activemask();  // both lanes of a pair are here or neither is
+          const int kbeg = (rs / c) * c;
+          const unsigned char* myrow = rows + (size_t)rs * p.row_stride;
+          const int my_vox = reinterpret_cast<const int*>(sp + kStageVoxOff)[rs];
+          const int2 me = *reinterpret_cast<const int2*>(myrow + data_bytes);
+          for (int hi = 0; hi < n_hiter; ++hi) {
+            const int h = hi * p.HG + hgs;
+            RowState<HH> hs;
+            load_q_smem<HH>(reinterpret_cast<const float4*>(myrow) + (h * HD + x * HH) / 4, qscale, hs.q);
+            hs.reset();
+            const float* table_h = table_base + (me.y >> 8) * H + h;
+            if (p.use_mask)
+              attend_keys_split<HH, kTableSmem, true>(hs, rows, p.row_stride, data_bytes, kbeg, c,
+                                                      (C + h * HD + x * HH) * 4, C, table_h, me.y & 31, lanes);
+            else
+              attend_keys_split<HH, kTableSmem, false>(hs, rows, p.row_stride, data_bytes, kbeg, c,
+                                                       (C + h * HD + x * HH) * 4, C, table_h, 0, lanes);
+            store_out<T, HH>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD + x * HH, hs,
+                             1.0f / (hs.l + 1e-8f));
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+        continue;
+      }
       const bool row_active = thread_used && r < q_rows;
       const int wl = r / c;
       const int kbeg = wl * c;
@@ -555,14 +664,14 @@ struct KernelShape {
 static int table_entries(const int32_t w[3], int heads) {
   return (2 * w[0] - 1) * (2 * w[1] - 1) * (2 * w[2] - 1) * heads;
 }
-static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, const int32_t rpb_window[3]) {
+static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, const int32_t rpb_window[3], bool split = false) {
   KernelShape s;
   int cap = 256 / tile;
   if (cap < 1) cap = 1;
   s.hg = 1;
   for (int g = 1; g <= heads && g <= cap; ++g)
     if (heads % g == 0) s.hg = g;
-  s.group_threads = (tile * s.hg + 31) & ~31;
+  s.group_threads = ((split ? 2 * tile : tile) * s.hg + 31) & ~31;
   const int C = heads * head_dim;
   s.row_stride = 3 * C * 4 + 16;  // +16 B skews rows across shared-memory banks
   const int rows_bytes = kStageRowsOff + tile * s.row_stride;
@@ -583,7 +692,7 @@ static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, cons
     const int v = atoi(e);
     if (v >= 1 && v <= kMaxProducerWarps) s.prod_warps = v;
   }
-  while (groups > 1 && groups * s.group_threads + 32 * s.prod_warps > 1024) --groups;
+  while (groups > 1 && groups * s.group_threads + 32 * s.prod_warps > (split ? 768 : 1024)) --groups;
   if (groups < 1) groups = 1;
   // Tuning overrides (experiments only): SSW_STAGES / SSW_GROUPS within the shared-memory budget.
   if (const char* e = getenv("SSW_STAGES")) {
@@ -604,16 +713,27 @@ static int launch_attn(const AttnParams& p, int threads, size_t smem, cudaStream
   int dev = 0, sms = 0;
   SSW_CUDA_TRY(cudaGetDevice(&dev));
   SSW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  if constexpr (sizeof(T) == 4) {
+    if (p.split) {
+      if (threads > 768) return SSW_E_UNSUPPORTED;
+      void (*kern)(AttnParams) = threads <= 640 ? k_attn_fused<T, HD, kTableSmem, 640, true>
+                                                : k_attn_fused<T, HD, kTableSmem, 768, true>;
+      SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), smem, stream, p));
+      SSW_LAUNCH_CHECK("k_attn_fused");
+      return SSW_OK;
+    }
+  }
   if (threads <= 384) {
-    auto kern = k_attn_fused<T, HD, kTableSmem, 384>;
+    auto kern = k_attn_fused<T, HD, kTableSmem, 384, false>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), smem, stream, p));
   } else if (threads <= 512) {
-    auto kern = k_attn_fused<T, HD, kTableSmem, 512>;
+    auto kern = k_attn_fused<T, HD, kTableSmem, 512, false>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), smem, stream, p));
   } else {
-    auto kern = k_attn_fused<T, HD, kTableSmem, 1024>;
+    auto kern = k_attn_fused<T, HD, kTableSmem, 1024, false>;
     SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), smem, stream, p));
   }
@@ -688,8 +808,16 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
     if (elt != 2 || attn_vals) return SSW_E_INVALID;
     return run_attn_mma(p, dtype, head_dim, rpb_window, stream);
   }
-  const KernelShape s = kernel_shape(tile, heads, head_dim, elt, rpb_window);
+  // fp32 without the COO output: the channels of a (row, head) are split over a lane pair
+  bool split = dtype == SSW_F32 && !attn_vals && head_dim % 8 == 0;
+  if (const char* e = getenv("SSW_SPLIT")) split = split && atoi(e) != 0;  // tuning override (experiments only)
+  KernelShape s = kernel_shape(tile, heads, head_dim, elt, rpb_window, split);
+  if (split && s.groups * s.group_threads + 32 * s.prod_warps > 768) {
+    split = false;
+    s = kernel_shape(tile, heads, head_dim, elt, rpb_window, false);
+  }
   if (s.stages < 2 || s.smem > 227 * 1024) return SSW_E_UNSUPPORTED;
+  p.split = split ? 1 : 0;
   const int threads = s.groups * s.group_threads + 32 * s.prod_warps;
   p.HG = s.hg;
   p.group_threads = s.group_threads;

@@ -66,7 +66,8 @@ def test_bucket_and_fused_fp32(shift, from_coords):
     assert rel_err(attn.cpu(), attn_ref.values) <= FP32_TOL
     out2 = attention.window_attention_fused(case["qkv"].to(dev), plan, case["table"].to(dev), case["scale"],
                                             use_mask=case["mask"] is not None)
-    assert torch.equal(out2, out)  # the emitting variant and the plain one agree bit for bit
+    # the emitting variant keeps a whole head per thread, the plain one splits it over a lane pair
+    assert rel_err(out2.cpu(), out.cpu()) <= 2e-6
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, BF16_TOL), (torch.float16, 2e-3)])
