@@ -369,6 +369,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     }
     for (int g = 0; g < G; ++g) mbar_init(gbar + g, gwarps);
     mbar_init(bbar, 1);
+    mbar_init(bbar + 1, 1);
     mbar_init(tbar, 1);
     mbar_fence_init();
   }
@@ -573,11 +574,16 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   // ------------------------------------------------------------------------------------------
   // Phase B: windows with c > tile; one query tile per item, key tiles through stage 0
   // ------------------------------------------------------------------------------------------
-  unsigned char* rows = stage0 + kStageRowsOff;
-  uint32_t phase = 0;
-  const int hg = threadIdx.x / tile;
-  const int r = threadIdx.x - hg * tile;
-  const bool thread_used = hg < p.HG;  // the first tile*HG threads do the arithmetic
+  // Key tiles alternate between stages 0 and 1: the copy of the next tile is in flight while the
+  // current one is used.  In the lane-pair form two adjacent threads share a (row, head).
+  constexpr int HB = kSplit ? HD / 2 : HD;  // channels per thread
+  const int xh = kSplit ? (int)(threadIdx.x & 1) : 0;
+  const int rh = kSplit ? (int)(threadIdx.x >> 1) : (int)threadIdx.x;
+  const int hg = rh / tile;
+  const int r = rh - hg * tile;
+  const bool thread_used = hg < p.HG;
+  uint64_t* tbars[2] = {bbar, bbar + 1};
+  uint32_t tphase[2] = {0, 0};
   for (int item = n_small + blockIdx.x; item < n_items; item += gridDim.x) {
     const int4 d = __ldg(p.pack_desc + item);
     const int c = d.y;
@@ -594,13 +600,29 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     }
     const int n_tiles = (c + tile - 1) / tile;
     const int n_pass = p.attn_vals ? 2 : 1;
+    const int n_seq = n_pass * n_tiles;
+    auto issue_tile = [&](int q) {  // key tile q % n_tiles into buffer q & 1
+      const int k0 = (q % n_tiles) * tile;
+      const int rows_t = min(tile, c - k0);
+      unsigned char* rb = stage0 + (size_t)(q & 1) * p.stage_bytes + kStageRowsOff;
+      if (threadIdx.x == 0) mbar_expect_tx(tbars[q & 1], rows_t * copy_bytes);
+      if ((int)threadIdx.x < rows_t) {
+        const int row = d.x + k0 + threadIdx.x;
+        const int vj = __ldg(p.pack_perm + row);
+        const int km = __ldg(p.pack_meta + row);
+        *reinterpret_cast<int2*>(rb + (size_t)threadIdx.x * p.row_stride + data_bytes) =
+            make_int2(meta_rel(km) * H * 4, meta_region(km));
+        bulk_g2s(rb + (size_t)threadIdx.x * p.row_stride + copy_off,
+                 reinterpret_cast<const T*>(p.qkv) + (int64_t)vj * 3 * C, copy_bytes, tbars[q & 1]);
+      }
+    };
     for (int hi = 0; hi < n_hiter; ++hi) {
       const int h = hi * p.HG + hg;
-      RowState<HD> st;
+      RowState<HB> st;
       st.reset();
       float inv_l = 0.f;
       if (row_active)
-        load_q_global<T, HD>(reinterpret_cast<const T*>(p.qkv) + (int64_t)my_vox * 3 * C + h * HD, qscale, st.q);
+        load_q_global<T, HB>(reinterpret_cast<const T*>(p.qkv) + (int64_t)my_vox * 3 * C + h * HD + xh * HB, qscale, st.q);
       const float* table_h = table_base + my_rel + h;
       T* emit = nullptr;
       if (n_pass == 2 && row_active) {
@@ -608,45 +630,48 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
         emit = reinterpret_cast<T*>(p.attn_vals) + ((int64_t)__ldg(p.coo_start + kwin) * H + (int64_t)h * c * c) +
                (int64_t)(q_first + r) * c;
       }
-      for (int pass = 0; pass < n_pass; ++pass) {
-        for (int t = 0; t < n_tiles; ++t) {
-          const int k0 = t * tile;
-          const int rows_t = min(tile, c - k0);
-          if (threadIdx.x == 0) mbar_expect_tx(bbar, rows_t * copy_bytes);
-          if ((int)threadIdx.x < rows_t) {
-            const int row = d.x + k0 + threadIdx.x;
-            const int vj = __ldg(p.pack_perm + row);
-            const int km = __ldg(p.pack_meta + row);
-            *reinterpret_cast<int2*>(rows + (size_t)threadIdx.x * p.row_stride + data_bytes) =
-                make_int2(meta_rel(km) * H * 4, meta_region(km));
-            bulk_g2s(rows + (size_t)threadIdx.x * p.row_stride + copy_off,
-                     reinterpret_cast<const T*>(p.qkv) + (int64_t)vj * 3 * C, copy_bytes, bbar);
-          }
-          __syncthreads();  // row metadata visible
-          const bool ok = mbar_wait_bounded(bbar, phase);
-          if (__syncthreads_or(!ok)) {
-            if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
-            return;
-          }
-          phase ^= 1;
-          if constexpr (kHalf)
-            widen_rows<T>(rows, p.row_stride, row_elems, rows_t, threadIdx.x, blockDim.x, []() {
-              __syncthreads();
-              return true;
-            });
-          if (row_active) {
-            if (pass == 0)
+      issue_tile(0);
+      for (int q = 0; q < n_seq; ++q) {
+        const int b = q & 1;
+        const int k0 = (q % n_tiles) * tile;
+        const int rows_t = min(tile, c - k0);
+        unsigned char* rows = stage0 + (size_t)b * p.stage_bytes + kStageRowsOff;
+        if (q + 1 < n_seq) issue_tile(q + 1);  // its buffer was released by the barrier that ended tile q-1
+        __syncthreads();                        // row metadata of tile q visible
+        const bool ok = mbar_wait_bounded(tbars[b], tphase[b]);
+        if (__syncthreads_or(!ok)) {
+          if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
+          return;
+        }
+        tphase[b] ^= 1;
+        if constexpr (kHalf)
+          widen_rows<T>(rows, p.row_stride, row_elems, rows_t, threadIdx.x, blockDim.x, []() {
+            __syncthreads();
+            return true;
+          });
+        if (row_active) {
+          if constexpr (kSplit) {
+            const unsigned lanes = __activemask();  // both lanes of a pair are here or neither is
+            if (p.use_mask)
+              attend_keys_split<HB, kTableSmem, true>(st, rows, p.row_stride, data_bytes, 0, rows_t,
+                                                      (C + h * HD + xh * HB) * 4, C, table_h, my_region, lanes);
+            else
+              attend_keys_split<HB, kTableSmem, false>(st, rows, p.row_stride, data_bytes, 0, rows_t,
+                                                       (C + h * HD + xh * HB) * 4, C, table_h, my_region, lanes);
+          } else {
+            if (q < n_tiles)
               attend_keys_m<T, HD, false, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, 0, rows_t,
                                                       (C + h * HD) * 4, C, table_h, my_region, 0.f, (T*)nullptr);
             else
               attend_keys_m<T, HD, true, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, 0, rows_t,
                                                      (C + h * HD) * 4, C, table_h, my_region, inv_l, emit + k0);
           }
-          __syncthreads();  // everyone done with this tile before it is overwritten
         }
-        if (pass == 0) inv_l = 1.0f / (st.l + 1e-8f);
+        if (q == n_tiles - 1) inv_l = 1.0f / (st.l + 1e-8f);
+        __syncthreads();  // everyone done with this tile before it is overwritten
       }
-      if (row_active) store_out<T, HD>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD, st, inv_l);
+      if (row_active)
+        store_out<T, HB>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD + xh * HB, st, inv_l);
     }
   }
 }
