@@ -32,6 +32,7 @@ extern "C" {
 #define SSW_DEV_DUPLICATE 2u   /* two voxels share (window, pos); upstream forbids it   */
 #define SSW_DEV_COO_RANGE 4u   /* sum c^2 * H would not fit int32 (COO path unusable)   */
 #define SSW_DEV_TIMEOUT 8u     /* a bounded wait on an async copy gave up               */
+#define SSW_DEV_BAD_PLAN 16u   /* the plan handed to an attention kernel is inconsistent */
 
 /* ---- element types --------------------------------------------------------------- */
 #define SSW_F32 0

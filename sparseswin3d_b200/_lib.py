@@ -16,7 +16,7 @@ SSW_F32, SSW_BF16, SSW_F16 = 0, 1, 2
 HEADER_INTS = 64
 H_N, H_W, H_PACKS, H_ERROR, H_CMAX, H_SUMC2_LO, H_SUMC2_HI, H_TILE = range(8)
 H_PACKS_SMALL, H_PADDED = 10, 11
-DEV_BAD_COORD, DEV_DUPLICATE, DEV_COO_RANGE, DEV_TIMEOUT = 1, 2, 4, 8
+DEV_BAD_COORD, DEV_DUPLICATE, DEV_COO_RANGE, DEV_TIMEOUT, DEV_BAD_PLAN = 1, 2, 4, 8, 16
 
 i32, i64, vp, f32 = C.c_int32, C.c_int64, C.c_void_p, C.c_float
 I3 = i32 * 3

@@ -30,6 +30,7 @@ struct AttnParams {
   int group_threads;  // threads of one consumer group (multiple of 32) = ceil32(tile * HG)
   int groups, stages;
   int prod_warps;     // warps that issue the row copies of an item
+  int n_vox, pack_cap;  // bounds the kernels hold the plan's voxel ids and item counts to
   int split;          // CUDA-core kernel: a (row, head) is shared by two lanes, half the channels each
   float scale;
   int use_mask;
@@ -40,6 +41,31 @@ struct AttnParams {
 };
 
 
+
+// The attention kernels turn plan entries into addresses.  A plan that is stale or was overwritten
+// must not become a wild access: entries are held to their bounds, violations set SSW_DEV_BAD_PLAN
+// and are replaced by harmless values (the output is then meaningless, and flagged).
+__device__ __forceinline__ int checked_voxel(int v, const AttnParams& p) {
+  if ((unsigned)v < (unsigned)p.n_vox) return v;
+  atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_BAD_PLAN);
+  return 0;
+}
+// pack descriptor {first row, c, windows (or -(tile index)-1), window slot}
+__device__ __forceinline__ int4 checked_desc(int4 d, const AttnParams& p) {
+  const bool pack = d.z >= 0;
+  // 32-bit arithmetic is safe here: every product is formed only after its factors are known small
+  bool ok = (unsigned)d.x < (unsigned)p.n_vox && (unsigned)(d.y - 1) < 1023u;
+  if (pack) ok = ok && d.z <= p.tile && d.z * d.y <= p.tile && d.z * d.y <= p.n_vox - d.x;
+  else ok = ok && d.y <= p.n_vox - d.x && -d.z - 1 <= d.y / p.tile;
+  if (ok) return d;
+  atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_BAD_PLAN);
+  return pack ? make_int4(0, 1, 0, 0) : make_int4(0, 1, -1, 0);  // an empty pack / a one-row window
+}
+__device__ __forceinline__ int checked_count(int n, const AttnParams& p) {
+  if ((unsigned)n <= (unsigned)p.pack_cap) return n;
+  atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_BAD_PLAN);
+  return 0;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;

@@ -377,8 +377,8 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   // Only the barrier set-up may run ahead of the kernel this launch is chained behind: the plan,
   // qkv and the bias table may all have been written by it.
   grid_dependency_wait();
-  const int n_small = p.header[SSW_H_PACKS_SMALL];
-  const int n_items = p.header[SSW_H_PACKS];
+  const int n_items = checked_count(p.header[SSW_H_PACKS], p);
+  const int n_small = min(checked_count(p.header[SSW_H_PACKS_SMALL], p), n_items);
   if constexpr (kTableSmem) {
     if (!is_producer) {  // the producers are already gathering the first items
       table_ok = stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons, tbar);
@@ -422,7 +422,10 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     for (int a = 0; a <= kAhead + 1; ++a)
       dq[a] = a < my_items ? __ldg(p.pack_desc + item_index(a)) : make_int4(0, 0, 0, 0);
 #pragma unroll
-    for (int a = 0; a < kAhead; ++a) fetch(dq[a], vox[a], km[a]);
+    for (int a = 0; a < kAhead; ++a) {
+      if (a < my_items) dq[a] = checked_desc(dq[a], p);
+      fetch(dq[a], vox[a], km[a]);
+    }
     for (int i = 0; i < my_items; ++i) {
       const int s = i % S;
       const int use = i / S;
@@ -430,7 +433,9 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
                              ? __ldg(p.pack_desc + item_index(i + kAhead + 2))
                              : make_int4(0, 0, 0, 0);
       int vox_n[2], km_n[2];
-      fetch(dq[kAhead], vox_n, km_n);  // item i + kAhead (an all-zero descriptor fetches nothing)
+      // the descriptor of item i + kAhead arrived iterations ago: checking it here waits for nothing
+      if (i + kAhead < my_items) dq[kAhead] = checked_desc(dq[kAhead], p);
+      fetch(dq[kAhead], vox_n, km_n);  // (an all-zero descriptor fetches nothing)
       if (use > 0 && !mbar_wait_bounded(empty + s, (use - 1) & 1)) {
         timed_out = true;
         break;
@@ -443,6 +448,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       for (int k = 0; k < 2; ++k) {
         const int rr = (lane + 32 * k) * PW + pw;
         if (rr < nr) {
+          vox[0][k] = checked_voxel(vox[0][k], p);  // loaded three items ago: no wait
           reinterpret_cast<int*>(st + kStageVoxOff)[rr] = vox[0][k];
           *reinterpret_cast<int2*>(st + kStageRowsOff + (size_t)rr * p.row_stride + data_bytes) = make_int2(
               meta_rel(km[0][k]) * H * 4, meta_region(km[0][k]) | ((meta_rel(km[0][k]) + p.rel_off) << 8));
@@ -585,7 +591,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   uint64_t* tbars[2] = {bbar, bbar + 1};
   uint32_t tphase[2] = {0, 0};
   for (int item = n_small + blockIdx.x; item < n_items; item += gridDim.x) {
-    const int4 d = __ldg(p.pack_desc + item);
+    const int4 d = checked_desc(__ldg(p.pack_desc + item), p);
     const int c = d.y;
     const int q_first = (-d.z - 1) * tile;
     const int q_rows = min(tile, c - q_first);
@@ -593,7 +599,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     int my_vox = 0, my_rel = 0, my_region = 0;
     if (row_active) {
       const int row = d.x + q_first + r;
-      my_vox = __ldg(p.pack_perm + row);
+      my_vox = checked_voxel(__ldg(p.pack_perm + row), p);
       const int m = __ldg(p.pack_meta + row);
       my_rel = (meta_rel(m) + p.rel_off) * H;
       my_region = meta_region(m);
@@ -608,7 +614,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       if (threadIdx.x == 0) mbar_expect_tx(tbars[q & 1], rows_t * copy_bytes);
       if ((int)threadIdx.x < rows_t) {
         const int row = d.x + k0 + threadIdx.x;
-        const int vj = __ldg(p.pack_perm + row);
+        const int vj = checked_voxel(__ldg(p.pack_perm + row), p);
         const int km = __ldg(p.pack_meta + row);
         *reinterpret_cast<int2*>(rb + (size_t)threadIdx.x * p.row_stride + data_bytes) =
             make_int2(meta_rel(km) * H * 4, meta_region(km));
@@ -828,6 +834,8 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   p.tile = tile;
   p.scale = scale;
   p.use_mask = use_mask;
+  p.n_vox = (int)L->n_vox;
+  p.pack_cap = (int)L->pack_cap;
   if (L->padded) {
     // padded plan: the tensor-core kernel takes both the packs and the windows beyond a pack
     if (elt != 2 || attn_vals) return SSW_E_INVALID;

@@ -278,8 +278,8 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   fence_async_smem();  // order the zero fill before the bulk copies that will land in the same rows
   __syncthreads();
   grid_dependency_wait();
-  const int n_small = p.header[SSW_H_PACKS_SMALL];
-  const int n_items = p.header[SSW_H_PACKS];
+  const int n_items = checked_count(p.header[SSW_H_PACKS], p);
+  const int n_small = min(checked_count(p.header[SSW_H_PACKS_SMALL], p), n_items);
   if constexpr (kTableSmem) {
     if (!is_producer) {  // the producers are already gathering the first items
       table_ok = stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons, tbar);
@@ -324,7 +324,10 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
     for (int a = 0; a <= kAhead + 1; ++a)
       dq[a] = a < my_items ? __ldg(p.pack_desc + item_index(a)) : make_int4(0, 0, 0, 0);
 #pragma unroll
-    for (int a = 0; a < kAhead; ++a) fetch(dq[a], vox[a], km[a]);
+    for (int a = 0; a < kAhead; ++a) {
+      if (a < my_items) dq[a] = checked_desc(dq[a], p);
+      fetch(dq[a], vox[a], km[a]);
+    }
     for (int i = 0; i < my_items; ++i) {
       const int s = i % S;
       const int use = i / S;
@@ -332,7 +335,9 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
                              ? __ldg(p.pack_desc + item_index(i + kAhead + 2))
                              : make_int4(0, 0, 0, 0);
       int vox_n[2], km_n[2];
-      fetch(dq[kAhead], vox_n, km_n);  // item i + kAhead (an all-zero descriptor fetches nothing)
+      // the descriptor of item i + kAhead arrived iterations ago: checking it here waits for nothing
+      if (i + kAhead < my_items) dq[kAhead] = checked_desc(dq[kAhead], p);
+      fetch(dq[kAhead], vox_n, km_n);  // (an all-zero descriptor fetches nothing)
       if (use > 0 && !mbar_wait_bounded(empty + s, (use - 1) & 1)) {
         timed_out = true;
         break;
@@ -344,6 +349,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
       for (int k = 0; k < 2; ++k) {
         const int slot = (lane + 32 * k) * PW + pw;
         if (slot < tile) {
+          if (vox[0][k] >= 0) vox[0][k] = checked_voxel(vox[0][k], p);  // loaded three items ago: no wait
           reinterpret_cast<int*>(st + kMmaStageVoxOff)[slot] = vox[0][k];
           // Unused slots form a window of their own with neutral codes, so their (discarded) scores
           // index inside the bias table.
@@ -431,7 +437,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   unsigned char* q_rows = q_stage + kMmaStageRowsOff;
   int kseq = 0, qseq = 0;  // key tiles / query tiles handled so far by this CTA
   for (int item = n_small + blockIdx.x; item < n_items && !timed_out; item += gridDim.x, ++qseq) {
-    const int4 d = __ldg(p.pack_desc + item);
+    const int4 d = checked_desc(__ldg(p.pack_desc + item), p);
     const int c = d.y;
     const int q_first = (-d.z - 1) * tile;
     const int n_q = min(tile, c - q_first);
@@ -445,7 +451,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
         qv[k] = -1;
         qm[k] = 0;
         if (slot < n_q) {
-          qv[k] = __ldg(p.pack_perm + d.x + q_first + slot);
+          qv[k] = checked_voxel(__ldg(p.pack_perm + d.x + q_first + slot), p);
           qm[k] = __ldg(p.pack_meta + d.x + q_first + slot);
         }
       }
@@ -485,7 +491,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
           kv[k] = -1;
           kmeta[k] = 0;
           if (slot < n_k) {
-            kv[k] = __ldg(p.pack_perm + d.x + k0 + slot);
+            kv[k] = checked_voxel(__ldg(p.pack_perm + d.x + k0 + slot), p);
             kmeta[k] = __ldg(p.pack_meta + d.x + k0 + slot);
           }
         }

@@ -113,6 +113,8 @@ class WindowPlan:
             raise _lib.SswError("two voxels share (window, pos): coordinates must be unique")
         if e & _lib.DEV_TIMEOUT:
             raise _lib.SswError("device-side wait on an async copy timed out")
+        if e & _lib.DEV_BAD_PLAN:
+            raise _lib.SswError("an attention kernel was handed an inconsistent plan (stale or overwritten buffer)")
 
     def occupancy(self) -> torch.Tensor:
         """`_c` of upstream at window granularity (int32 [W]).  Synchronises."""
