@@ -87,3 +87,24 @@ def test_batch_of_scenes_with_full_and_singleton_windows(dtype, tol):
     assert st["c_max"] == int(counts.max()) and st["windows"] == counts.size
     out = attention.window_attention_fused(qkv.to(dev), plan, table.to(dev), 32 ** -0.5, use_mask=True)
     assert rel_err(out.float().cpu(), ref) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_overwritten_plan_is_flagged_not_followed(dtype):
+    """A plan buffer whose voxel ids were overwritten (a stale or recycled buffer): the attention
+    kernel must not use them as addresses; it sets SSW_DEV_BAD_PLAN and finishes."""
+    from sparseswin3d_b200 import _lib, attention, window
+
+    dev = torch.device("cuda:0")
+    case = make_case(n_vox=1200, grid=24, seed=8)
+    geom = window.resolve_geometry(1, case["dims"], case["window"], case["shift"])
+    plan = window.bucket_windows(coords=case["coords"].to(dev), geom=geom, **attention.plan_params(3, 32, dtype))
+    assert plan.stats()["error"] == 0
+    plan.pack_perm[::7] = 2 ** 30          # far outside [0, N)
+    plan.pack_perm[3::11] = -5
+    out = attention.window_attention_fused(case["qkv"].to(dtype).to(dev), plan, case["table"].to(dev), case["scale"])
+    torch.cuda.synchronize()
+    assert out.shape == (1200, 96)
+    assert plan.stats()["error"] & _lib.DEV_BAD_PLAN
+    with pytest.raises(_lib.SswError):
+        plan.raise_on_error()
