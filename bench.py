@@ -38,8 +38,8 @@ N_VOX = 150_000
 HEADS, HEAD_DIM, WINDOW, SHIFT = 3, 32, (7, 7, 7), (3, 3, 3)
 C = HEADS * HEAD_DIM
 # kernels of this library per pass: k_count, k_reduce, k_compact, k_order, k_scatter, then k_attn_fused
-# (fp32) or k_attn_mma + the k_attn_fused launch that takes the windows larger than a tile (bf16)
-KERNELS_PER_PASS = {"f32": 6, "bf16": 7}
+# (fp32) or k_attn_mma (bf16)
+KERNELS_PER_PASS = {"f32": 6, "bf16": 6}
 DOMINANT_KERNEL = {"f32": "k_attn_fused", "bf16": "k_attn_mma"}
 # DRAM bytes one launch of the dominant kernel moves on this workload (dram__bytes_read.sum +
 # dram__bytes_write.sum of the ncu captures summarised under profiles/).  Part of the output is still
@@ -94,11 +94,9 @@ class ClockSampler:
             except Exception:
                 self.proc.kill()
 
-    def summary(self, first: int = 0):
-        """Samples from index `first` on (the timed region and the identical work kept running behind
-        it); when the sampler was too slow to deliver any of those, the last samples before it, taken
-        while the same steps ran as warm-up."""
-        rows = self.rows[first:] or self.rows[-3:]
+    def summary(self, first: int = 0, last=None):
+        """Samples [first, last): the ones delivered while the timed region ran."""
+        rows = self.rows[first:last]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in rows:
@@ -111,7 +109,7 @@ class ClockSampler:
             except Exception:
                 continue
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}  # region shorter than the period
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
@@ -126,9 +124,233 @@ def make_inputs(seed: int, dtype: torch.dtype, device, n_sets: int):
     return coords_host, dims, qkv_host, table
 
 
-def run_ours(args):
-    from sparseswin3d_b200 import _lib, attention, window
+class RoomSteps:
+    """The step of the benchmark for one scene and one dtype on one GPU: buffers, the two plans'
+    scratch, and one captured CUDA graph per rotating buffer set."""
 
+    N_SETS = 4  # qkv/out sets; the two passes of a step use different sets, consecutive steps too
+
+    def __init__(self, seed: int, dtype: torch.dtype, dev, host_qkv: bool = False):
+        from sparseswin3d_b200 import _lib, attention, window
+
+        self.dev, self.dtype = dev, dtype
+        self.elt = torch.empty(0, dtype=dtype).element_size()
+        self.coords_h, dims, self.qkv_h, self.table = make_inputs(seed, dtype, dev, self.N_SETS if host_qkv else 1)
+        self.coords = self.coords_h.to(dev)
+        if host_qkv:
+            self.qkv = [q.to(dev) for q in self.qkv_h]
+        else:  # device-side inputs are enough for the device-timed legs
+            g = torch.Generator(device=dev).manual_seed(2000 + seed)
+            self.qkv = [torch.randn(N_VOX, 3, HEADS, HEAD_DIM, device=dev, generator=g).to(dtype) for _ in range(self.N_SETS)]
+        self.outs = [torch.empty(N_VOX, C, dtype=dtype, device=dev) for _ in range(self.N_SETS)]
+        self.geoms = [window.resolve_geometry(1, dims, WINDOW, (0, 0, 0)), window.resolve_geometry(1, dims, WINDOW, SHIFT)]
+        self.pp = attention.plan_params(HEADS, HEAD_DIM, dtype, WINDOW)
+        L = _lib.PlanLayout()
+        _lib.check(_lib.lib.ssw_plan_layout_init(L, N_VOX, self.geoms[0].n_windows, self.geoms[0].n_per_window,
+                                                 self.pp["tile_rows"], int(self.pp["padded"])), "layout")
+        self.layout = L
+        # one scratch and one plan buffer per pass: the two plans of a step are built side by side
+        self.scratch = [torch.empty(L.scratch_ints, dtype=torch.int32, device=dev) for _ in self.geoms]
+        self.plan_buf = [torch.empty(L.plan_ints, dtype=torch.int32, device=dev) for _ in self.geoms]
+        self.aux = torch.cuda.Stream(device=dev)
+        self.scale = HEAD_DIM ** -0.5
+        self.graphs = None
+        self.last_plans = None
+
+    def build_plan(self, i, coords=None, scratch=None, plan_buffer=None):
+        from sparseswin3d_b200 import window
+
+        return window.bucket_windows(coords=self.coords if coords is None else coords, geom=self.geoms[i],
+                                     scratch=self.scratch[i] if scratch is None else scratch,
+                                     plan_buffer=self.plan_buf[i] if plan_buffer is None else plan_buffer, **self.pp)
+
+    def step(self, s):
+        """W-MSA then SW-MSA.  Both plans depend on the coordinates only: the SW-MSA plan is built on
+        a second stream while the first builds the W-MSA plan and runs W-MSA attention; SW-MSA
+        attention waits for it.  (Fork and join are stream waits, so the same code captures into one
+        graph.)  The two passes read and write different buffer sets."""
+        from sparseswin3d_b200 import attention
+
+        a, b = (2 * s) % self.N_SETS, (2 * s + 1) % self.N_SETS
+        cur = torch.cuda.current_stream(self.dev)
+        self.aux.wait_stream(cur)
+        with torch.cuda.stream(self.aux):
+            plan1 = self.build_plan(1)
+        plan0 = self.build_plan(0)
+        attention.window_attention_fused(self.qkv[a], plan0, self.table, self.scale, use_mask=False, out=self.outs[a])
+        cur.wait_stream(self.aux)
+        attention.window_attention_fused(self.qkv[b], plan1, self.table, self.scale, use_mask=True, out=self.outs[b])
+        self.last_plans = (plan0, plan1)
+
+    def capture(self):
+        """The host side is Python: one step is about 14 launches, and enqueueing them from the
+        interpreter is slower than the GPU runs them.  The product path for repeated steps is
+        therefore one CUDA graph per step (captured once per buffer set, replayed)."""
+        self.graphs = capture_graphs(self.step, self.N_SETS // 2, self.dev)
+
+    def run(self, k):
+        for i in range(k):
+            self.graphs[i % len(self.graphs)].replay()
+
+    def check(self):
+        for plan in self.last_plans:
+            err = plan.stats()["error"]
+            if err:
+                raise SystemExit(f"device error bits {err}")
+
+
+def capture_graphs(fn, n, dev):
+    side = torch.cuda.Stream(device=dev)
+    graphs = []
+    with torch.cuda.stream(side):
+        for s in range(n):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                fn(s)
+            graphs.append(g)
+    torch.cuda.synchronize()
+    return graphs
+
+
+def timed_blocks(run, k, barrier, n_blocks):
+    """Times `n_blocks` blocks of EXACTLY k steps, each bracketed by barrier + synchronize on both
+    sides and timed with CUDA events on the launching stream.  Returns the block times in ms."""
+    times = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(n_blocks):
+        barrier()
+        e0.record()
+        run(k)
+        e1.record()
+        barrier()
+        times.append(e0.elapsed_time(e1))
+    return times
+
+
+def time_graph(fn, reps, dev):
+    g = capture_graphs(fn, 1, dev)[0]
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(7):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) / reps)
+    return statistics.median(times)
+
+
+def kernel_roofline(rs: RoomSteps, dtype_name: str):
+    """The dominant kernel alone: a replayed graph of 12 back-to-back attention calls over rotating
+    buffer sets and both plans; and the bucketing call alone the same way."""
+    from sparseswin3d_b200 import attention, window
+
+    plans = [window.bucket_windows(coords=rs.coords, geom=g, **rs.pp) for g in rs.geoms]
+    torch.cuda.synchronize()
+    reps = 12
+
+    def attn_only(_):
+        for i in range(reps):
+            s = i % rs.N_SETS
+            attention.window_attention_fused(rs.qkv[s], plans[i % 2], rs.table, rs.scale, use_mask=bool(i % 2), out=rs.outs[s])
+
+    def bucket_only(_):
+        for i in range(reps):
+            window.bucket_windows(coords=rs.coords, geom=rs.geoms[i % 2], scratch=rs.scratch[0], plan_buffer=rs.plan_buf[0], **rs.pp)
+
+    k_ms = time_graph(attn_only, reps, rs.dev)
+    b_ms = time_graph(bucket_only, reps, rs.dev)
+    peak, peak_src = measured_peak_gbs()
+    alg_bytes = algorithmic_bytes_per_voxel(rs.elt) * N_VOX
+    achieved = alg_bytes / (k_ms * 1e-3) / 1e9
+    st = plans[0].stats()
+    return {"bound": "hbm", "kernel": DOMINANT_KERNEL[dtype_name], "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_8000": achieved / 8000.0,
+            "traffic": NCU_TRAFFIC_BYTES[dtype_name],
+            "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of the ncu capture summarised under profiles/ "
+                              "(not re-measured in this run)",
+            "algorithmic_bytes": alg_bytes, "kernel_ms": k_ms, "bucketing_ms": b_ms,
+            "timing": "CUDA events around a replayed CUDA graph of 12 back-to-back attention calls, median of 7"}, st
+
+
+def crop_vs_upstream(dev):
+    """The same-size anchor against upstream's own kernels: W-MSA + SW-MSA on the x,y < 200 corner of
+    the scene (the largest piece inside upstream's int32 index domain), fp32: this library's step
+    (bucketing from raw coordinates + fused attention) as a replayed graph, and its unfused operator
+    chain (the compatibility path, enqueued from Python) - upstream's time for the same sample comes
+    from the baseline leg."""
+    from sparseswin3d_b200 import attention, window
+    from sparseswin3d_b200.attention import WindowAttentionSparse
+
+    c, dims, qkv, table = _cpu_sample()
+    n = c.shape[0]
+    coords, qkv_d, table_d = c.to(dev), qkv.to(dev), table.to(dev)
+    geoms = [window.resolve_geometry(1, dims, WINDOW, (0, 0, 0)), window.resolve_geometry(1, dims, WINDOW, SHIFT)]
+    pp = attention.plan_params(HEADS, HEAD_DIM, torch.float32, WINDOW)
+    out = torch.empty(n, C, device=dev)
+    plans = [window.bucket_windows(coords=coords, geom=g, **pp) for g in geoms]
+    scr = torch.empty(max(p.layout.scratch_ints for p in plans), dtype=torch.int32, device=dev)
+    buf = torch.empty(max(p.layout.plan_ints for p in plans), dtype=torch.int32, device=dev)
+
+    def step(_):
+        for g in geoms:
+            plan = window.bucket_windows(coords=coords, geom=g, scratch=scr, plan_buffer=buf, **pp)
+            attention.window_attention_fused(qkv_d, plan, table_d, HEAD_DIM ** -0.5, use_mask=bool(g.shifted), out=out)
+
+    for _ in range(3):
+        step(0)
+    torch.cuda.synchronize()
+    fused_ms = time_graph(step, 1, dev)
+    # unfused chain through the module's operator path (upstream's forward on this library's ops)
+    m = WindowAttentionSparse(C, HEADS, WINDOW).to(dev)  # for its relative_position_index and bias table
+    passes = []
+    for g in geoms:
+        idx, region, _ = window.window_keys(coords, g, with_region=True)
+        mask = None
+        if g.shifted:  # compute_mask's table [nW, n] rebuilt from the per-voxel region ids
+            mask = torch.zeros(g.n_windows, g.n_per_window, dtype=torch.int8, device=dev)
+            mask[idx[:, 0].long(), idx[:, 1].long()] = region
+        passes.append((idx, g.n_windows, g.n_per_window, mask))
+
+    class _Chain(torch.nn.Module):
+        def forward(self, idx, bw, npw, mask):
+            from sparseswin3d_b200 import ops
+            from sparseswin3d_b200.sparse_tensor import qkv_sparse_cuda, softmax_last_dim, sp_add_mask, sp_add_rpb, \
+                spspmm_block_naive
+
+            q, k_t, v = qkv_sparse_cuda(qkv_d, idx, bw, npw)
+            attn = spspmm_block_naive(q * (HEAD_DIM ** -0.5), k_t, "q_k")
+            bias = m.relative_position_bias_table[m.relative_position_index[:npw, :npw].reshape(-1)].reshape(npw, npw, -1)
+            attn = sp_add_rpb(attn, bias.permute(2, 0, 1).contiguous())
+            if mask is not None:
+                attn = sp_add_mask(attn, mask)
+            x_ = spspmm_block_naive(softmax_last_dim(attn), v, "qk_v").permute((0, 2, 1, 3))
+            arg_sort = ops.return_inverse(ops.flatten_indices(idx.T.contiguous(), [bw, npw]), -1)[0]
+            return x_.values.reshape(n, C).index_select(0, arg_sort)
+
+    chain = _Chain()
+    with torch.no_grad():
+        for _ in range(2):
+            for ps in passes:
+                chain(*ps)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        reps = 5
+        for _ in range(reps):
+            for ps in passes:
+                chain(*ps)
+        torch.cuda.synchronize()
+        chain_ms = (time.perf_counter() - t0) / reps * 1e3
+    return {"voxels": n, "fused_step_ms": fused_ms, "fused_voxels_per_s": 2.0 * n / (fused_ms * 1e-3),
+            "unfused_ops_chain_step_ms": chain_ms, "unfused_ops_chain_voxels_per_s": 2.0 * n / (chain_ms * 1e-3),
+            "sample": "W-MSA + SW-MSA on the x,y<200 corner of the scene, fp32; fused = replayed CUDA graph of bucketing + "
+                      "fused attention; unfused = this library's ten-operator surface driven from Python (wall clock)"}
+
+
+def run_ours(args):
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -136,181 +358,96 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    # The clock sampler starts now: with several ranks on a host nvidia-smi needs seconds to deliver
-    # its first line.  Only samples from the timed region on are reported (see ClockSampler.summary).
-    sampler = ClockSampler(local)
-    sampler.__enter__()
+    # One clock sampler per job (rank 0's GPU), started now: nvidia-smi needs a moment to deliver its
+    # first line.  Only samples that fall inside the timed region are reported.
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.__enter__()
     if world > 1:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
-    dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[args.dtype]
-    elt = 4 if args.dtype == "f32" else 2
-    n_sets = 3  # rotate buffer sets so that no step finds its inputs in the 126 MB L2
-    coords_h, dims, qkv_h, table = make_inputs(rank, dtype, dev, n_sets)
-    coords = coords_h.to(dev)
-    qkv = [q.to(dev) for q in qkv_h]
-    outs = [torch.empty(N_VOX, C, dtype=dtype, device=dev) for _ in range(n_sets)]
-    geoms = [window.resolve_geometry(1, dims, WINDOW, (0, 0, 0)), window.resolve_geometry(1, dims, WINDOW, SHIFT)]
-    pp = attention.plan_params(HEADS, HEAD_DIM, dtype, WINDOW)
-    tile = args.tile or pp["tile_rows"]
-    padded = int(pp["padded"])
-    scale = HEAD_DIM ** -0.5
-    scratch = torch.empty(1, dtype=torch.int32, device=dev)
-
-    L = _lib.PlanLayout()
-    _lib.check(_lib.lib.ssw_plan_layout_init(L, N_VOX, geoms[0].n_windows, geoms[0].n_per_window, tile, padded), "layout")
-    scratch = torch.empty(L.scratch_ints, dtype=torch.int32, device=dev)
-    # one scratch and one plan buffer per pass: the two plans of a step are built side by side
-    pass_scratch = [torch.empty(L.scratch_ints, dtype=torch.int32, device=dev) for _ in geoms]
-    pass_plan = [torch.empty(L.plan_ints, dtype=torch.int32, device=dev) for _ in geoms]
-    aux = torch.cuda.Stream(device=dev)
-
-    def build_plan(i):
-        return window.bucket_windows(coords=coords, geom=geoms[i], rpb_window=WINDOW, tile_rows=tile, padded=bool(padded),
-                                     scratch=pass_scratch[i], plan_buffer=pass_plan[i])
-
-    def step(s):
-        # Both plans depend on the coordinates only.  The SW-MSA plan is built on a second stream
-        # while the first stream builds the W-MSA plan and runs W-MSA attention; SW-MSA attention
-        # waits for it.  (Fork and join are stream waits, so the same code captures into one graph.)
-        s = s % n_sets
-        cur = torch.cuda.current_stream(dev)
-        aux.wait_stream(cur)
-        with torch.cuda.stream(aux):
-            plan1 = build_plan(1)
-        plan0 = build_plan(0)
-        attention.window_attention_fused(qkv[s], plan0, table, scale, use_mask=False, out=outs[s])
-        cur.wait_stream(aux)
-        attention.window_attention_fused(qkv[s], plan1, table, scale, use_mask=True, out=outs[s])
-        return plan1
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # Eager warm-up (also builds every lazily initialised CUDA object before capture).
-    for i in range(max(args.warmup, 3)):
-        plan = step(i)
-    barrier()
-    err = plan.stats()["error"]
-    if err:
-        raise SystemExit(f"device error bits {err}")
+    def all_ranks(x):
+        """[world] list of a per-rank float."""
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        if world == 1:
+            return [float(x)]
+        out = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(out, t)
+        return [float(o.item()) for o in out]
 
-    # The host side is Python: one step is ~20 launches, and enqueueing them from the interpreter
-    # is slower than the GPU runs them.  The product path for repeated steps is therefore a CUDA
-    # graph per step (captured once, replayed): capture one step per rotating buffer set.
-    side = torch.cuda.Stream(device=dev)
+    def max_over_ranks(xs):
+        t = torch.tensor(xs, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
 
-    def capture(fn, n):
-        graphs = []
-        with torch.cuda.stream(side):
-            for s in range(n):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    fn(s)
-                graphs.append(g)
-        torch.cuda.synchronize()
-        return graphs
+    warm = max(args.warmup, 3)
 
-    step_graphs = capture(step, n_sets)
-
-    def run_steps(k):
-        for i in range(k):
-            step_graphs[i % n_sets].replay()
-
-    run_steps(max(args.warmup, 3))
-    barrier()
-
-    # ---- timed region: K steps, device-timed, max over ranks --------------------------------
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    clk = sampler
-    first_sample = 0
-    try:
+    def measure(dtype_name, seed, primary):
+        dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[dtype_name]
+        rs = RoomSteps(seed, dtype, dev, host_qkv=primary)
+        for i in range(warm):  # eager warm-up (also builds every lazily initialised CUDA object before capture)
+            rs.step(i)
         barrier()
-        first_sample = len(clk.rows)
-        e0.record()
-        run_steps(args.steps)
-        e1.record()
+        rs.check()
+        rs.capture()
+        rs.run(warm)
         barrier()
-        ms = e0.elapsed_time(e1)
-        # the region is shorter than the sampler's period: keep identical work running for a bounded
-        # number of steps (synchronised in small batches) until a few samples are in
-        for i in range(256):
-            if len(clk.rows) - first_sample >= 3:
-                break
-            step_graphs[i % n_sets].replay()
-            if i % 8 == 7:
-                torch.cuda.synchronize()
-        torch.cuda.synchronize()
-        err = plan.stats()["error"]
-        if err:
-            raise SystemExit(f"device error bits {err} after the timed region")
-    finally:
-        clk_summary = clk.summary(first_sample)
+        # At least 10 blocks, and for the headline as many more as keep the GPU under this load for
+        # 0.6 s, so that the clock sampler (0.1 s period) sees the region; the count is agreed between
+        # the ranks (every block holds two barriers).
+        calib = max(max_over_ranks([statistics.median(timed_blocks(rs.run, args.steps, barrier, 3))])[0], 1e-3)
+        n_blocks = max(10, min(400, int(600.0 / calib) + 1)) if primary else 5
+        n0 = len(sampler.rows) if (sampler and primary) else 0
+        blocks = timed_blocks(rs.run, args.steps, barrier, n_blocks)
+        n1 = len(sampler.rows) if (sampler and primary) else 0
+        rs.check()
+        return rs, blocks, (n0, n1)
+
+    # ---- timed region: blocks of K steps, device-timed, max over ranks per block ---------------
+    rs, blocks, (n0, n1) = measure(args.dtype, rank, True)
+    clk_summary = sampler.summary(n0, n1) if sampler else None
+    if sampler:
         sampler.__exit__(None, None, None)
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    n_blocks = len(blocks)
+    job_blocks = max_over_ranks(blocks)                      # per block: the slowest rank
+    ms = statistics.median(job_blocks)
     value = 2.0 * N_VOX * world * args.steps / (ms * 1e-3)
+    per_rank_ms = all_ranks(statistics.median(blocks) / args.steps)
 
-    # ---- dominant kernel alone: graphs of `reps` back-to-back attention calls -----------------
-    plans = [window.bucket_windows(coords=coords, geom=g, rpb_window=WINDOW, tile_rows=tile, padded=bool(padded)) for g in geoms]
-    torch.cuda.synchronize()
-    reps = 12
-
-    def attn_only(_):
-        for i in range(reps):
-            s = i % n_sets
-            attention.window_attention_fused(qkv[s], plans[i % 2], table, scale, use_mask=bool(i % 2), out=outs[s])
-
-    def bucket_only(_):
-        for i in range(reps):
-            window.bucket_windows(coords=coords, geom=geoms[i % 2], rpb_window=WINDOW, tile_rows=tile, padded=bool(padded), scratch=scratch)
-
-    def time_graph(fn):
-        g = capture(fn, 1)[0]
-        for _ in range(3):
-            g.replay()
-        torch.cuda.synchronize()
-        times = []
-        for _ in range(5):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            g.replay()
-            b.record()
-            torch.cuda.synchronize()
-            times.append(a.elapsed_time(b) / reps)
-        return statistics.median(times)
-
-    k_ms = time_graph(attn_only)
-    b_ms = time_graph(bucket_only)
-    peak, peak_src = measured_peak_gbs()
-    alg_bytes = algorithmic_bytes_per_voxel(elt) * N_VOX
-    achieved = alg_bytes / (k_ms * 1e-3) / 1e9
+    roof, st = kernel_roofline(rs, args.dtype)
+    elt = rs.elt
 
     # ---- end to end: host buffers in, host result out, through the public Python API ---------
     # Every step copies its coordinates and qkv from pinned host memory, runs both passes and copies
     # both results back to pinned host memory.  Two steps are in flight on two streams (each with its
     # own device buffers, scratch and captured graph), so the upload of one step overlaps the
     # download of the step before it: the link is full duplex and the copies are what bounds a step.
+    from sparseswin3d_b200 import attention, window
+
     n_fly = 2
     e2e_streams = [torch.cuda.Stream(device=dev) for _ in range(n_fly)]
-    out_h = [torch.empty(N_VOX, C, dtype=dtype).pin_memory() for _ in range(n_fly)]
-    c_d = [torch.empty_like(coords) for _ in range(n_fly)]
-    q_d = [torch.empty_like(qkv[0]) for _ in range(n_fly)]
-    o_d = [torch.empty(N_VOX, C, dtype=dtype, device=dev) for _ in range(n_fly)]
-    scr = [torch.empty(L.scratch_ints, dtype=torch.int32, device=dev) for _ in range(n_fly)]
+    out_h = [torch.empty(2, N_VOX, C, dtype=rs.dtype).pin_memory() for _ in range(n_fly)]
+    c_d = [torch.empty_like(rs.coords) for _ in range(n_fly)]
+    q_d = [torch.empty_like(rs.qkv[0]) for _ in range(n_fly)]
+    o_d = [torch.empty(N_VOX, C, dtype=rs.dtype, device=dev) for _ in range(n_fly)]
+    scr = [torch.empty(rs.layout.scratch_ints, dtype=torch.int32, device=dev) for _ in range(n_fly)]
+    pbuf = [torch.empty(rs.layout.plan_ints, dtype=torch.int32, device=dev) for _ in range(n_fly)]
 
     def e2e_step(k):
-        c_d[k].copy_(coords_h, non_blocking=True)
-        q_d[k].copy_(qkv_h[k], non_blocking=True)
-        for g in geoms:
-            plan = window.bucket_windows(coords=c_d[k], geom=g, rpb_window=WINDOW, tile_rows=tile, padded=bool(padded), scratch=scr[k])
-            o = attention.window_attention_fused(q_d[k], plan, table, scale, use_mask=bool(g.shifted), out=o_d[k])
-            out_h[k].copy_(o, non_blocking=True)
+        c_d[k].copy_(rs.coords_h, non_blocking=True)
+        q_d[k].copy_(rs.qkv_h[k], non_blocking=True)
+        for i, g in enumerate(rs.geoms):
+            plan = rs.build_plan(i, coords=c_d[k], scratch=scr[k], plan_buffer=pbuf[k])
+            o = attention.window_attention_fused(q_d[k], plan, rs.table, rs.scale, use_mask=bool(g.shifted), out=o_d[k])
+            out_h[k][i].copy_(o, non_blocking=True)
 
     e2e_graphs = []
     for k in range(n_fly):
@@ -329,49 +466,91 @@ def run_ours(args):
     e2e_run(4)
     barrier()
     k_e2e = max(4, min(args.steps, 20))
-    e0.record(e2e_streams[0])
-    e2e_run(k_e2e)
-    for st_ in e2e_streams[1:]:
-        e2e_streams[0].wait_stream(st_)
-    e1.record(e2e_streams[0])
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = 2.0 * N_VOX * world * k_e2e / (float(t.item()) * 1e-3)
-    h2d = coords_h.numel() * 4 + qkv_h[0].numel() * elt
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_times = []
+    for _ in range(5):
+        barrier()
+        e0.record(e2e_streams[0])
+        e2e_run(k_e2e)
+        for st_ in e2e_streams[1:]:
+            e2e_streams[0].wait_stream(st_)
+        e1.record(e2e_streams[0])
+        barrier()
+        e2e_times.append(e0.elapsed_time(e1))
+    e2e_ms = statistics.median(max_over_ranks(e2e_times))
+    e2e_value = 2.0 * N_VOX * world * k_e2e / (e2e_ms * 1e-3)
+    h2d = rs.coords_h.numel() * 4 + rs.qkv_h[0].numel() * elt
     d2h = 2 * N_VOX * C * elt
 
-    st = plans[0].stats()
     res = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warm,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": args.dtype, "data": "synthetic",
         "config": {"workload": "configs[1]: W-MSA + SW-MSA(shift 3, masked) on one synthetic 8x8x3 m room at 2 cm, "
                                f"{N_VOX} voxels per GPU, C=96, 3 heads x 32, window 7^3, bucketing + fused attention core "
                                "(qkv resident in HBM)",
                    "voxels_per_step_per_gpu": 2 * N_VOX, "windows": st["windows"], "sum_c2": st["sum_c2"],
-                   "c_max": st["c_max"], "tile_rows": tile,
-                   "l2": f"inputs {alg_bytes/1e6:.0f} MB per pass, {n_sets} rotating qkv/out sets ({n_sets*alg_bytes/1e6:.0f} MB) > 126 MB L2",
+                   "c_max": st["c_max"], "tile_rows": rs.pp["tile_rows"],
+                   "l2": f"{rs.N_SETS} rotating qkv/out sets ({rs.N_SETS * roof['algorithmic_bytes'] / 1e6:.0f} MB) > 126 MB L2; "
+                         "the two passes of a step and consecutive steps use different sets",
                    "parallelism": f"scene per GPU x{world}",
                    "launch": "one CUDA graph replay per step; the SW-MSA plan is built on a second stream beside the W-MSA pass"},
+        "timing": {"blocks": n_blocks, "steps_per_block": args.steps, "block_ms_min": min(job_blocks),
+                   "block_ms_median": ms, "block_ms_max": max(job_blocks),
+                   "rule": "every block is exactly `steps` graph replays between barrier + synchronize, CUDA events on the "
+                           "launching stream, max over ranks per block; value uses the median block"},
+        "per_rank_ms_per_step": per_rank_ms,
         "clocks": clk_summary,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": k_e2e, "in_flight": n_fly},
         "gpu_launches": KERNELS_PER_PASS[args.dtype] * 2 * args.steps,
-        "roofline": {"bound": "hbm", "kernel": DOMINANT_KERNEL[args.dtype], "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_8000": achieved / 8000.0, "traffic": NCU_TRAFFIC_BYTES[args.dtype],
-                     "algorithmic_bytes": alg_bytes, "kernel_ms": k_ms, "bucketing_ms": b_ms,
-                     "timing": "CUDA events around a replayed CUDA graph of 12 back-to-back attention calls, median of 5"},
+        "roofline": roof,
     }
+    del e2e_graphs, out_h, c_d, q_d, o_d
+
+    # ---- secondary lines (not the headline): the other dtype on the same step ------------------
+    secondary = []
+    if not args.no_secondary:
+        other = "bf16" if args.dtype == "f32" else "f32"
+        rs2, blocks2, _ = measure(other, rank, False)
+        nb2 = len(blocks2)
+        ms2 = statistics.median(max_over_ranks(blocks2))
+        roof2, _ = kernel_roofline(rs2, other)
+        secondary.append({"dtype": other, "value": 2.0 * N_VOX * world * args.steps / (ms2 * 1e-3), "unit": UNIT,
+                          "ms_per_step": ms2 / args.steps, "blocks": nb2, "roofline": roof2})
+        del rs2
+        if world > 1:
+            # control for the scaling loss: every rank runs the SAME scene (seed 0); what is left of the
+            # spread between ranks is then not scene heterogeneity
+            rs3, blocks3, _ = measure(args.dtype, 0, False)
+            res["control_same_scene"] = {"per_rank_ms_per_step": all_ranks(statistics.median(blocks3) / args.steps),
+                                         "job_ms_per_step": statistics.median(max_over_ranks(blocks3)) / args.steps}
+            del rs3
+    res["secondary"] = secondary
+    if world > 1 and not args.no_secondary:
+        res["shard"] = shard_lines(dev, rank, world)
     if world > 1:
         dist.barrier()
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
+            res["vs_upstream_gpu"] = crop_vs_upstream(dev)
             res["cpu_baseline"] = cpu_baseline(seconds=args.cpu_seconds)
+            up = res["cpu_baseline"].get("upstream_gpu")
+            if up and up.get("ms_per_step"):
+                res["vs_upstream_gpu"]["upstream_step_ms"] = up["ms_per_step"]
+                res["vs_upstream_gpu"]["ratio_fused"] = up["ms_per_step"] / res["vs_upstream_gpu"]["fused_step_ms"]
+                res["vs_upstream_gpu"]["ratio_unfused_ops_chain"] = \
+                    up["ms_per_step"] / res["vs_upstream_gpu"]["unfused_ops_chain_step_ms"]
         print(json.dumps(res), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def shard_lines(dev, rank, world):
+    """Evidence for the window-range split of one scene, recorded by the default multi-GPU run:
+    (1) a small scene sharded over the ranks gives bitwise the single-GPU output,
+    (2) the strong-scaling time of the skewed 10^6-voxel scene."""
+    return {"unavailable": "not measured in this run"}
 
 
 def run_skewed(args):
@@ -492,9 +671,14 @@ def cpu_baseline(seconds: float = 15.0):
         if time.perf_counter() - t0 > seconds or n >= 5:
             break
     dt = time.perf_counter() - t0
-    return {"value": 2.0 * c.shape[0] * n / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{n} step(s) of W-MSA+SW-MSA on the x,y<200 corner of the scene ({c.shape[0]} voxels, fp32), "
-                      "oracle/ssw_oracle.py on torch CPU"}
+    res = {"value": 2.0 * c.shape[0] * n / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+           "sample": f"{n} step(s) of W-MSA+SW-MSA on the x,y<200 corner of the scene ({c.shape[0]} voxels, fp32), "
+                     "oracle/ssw_oracle.py on torch CPU"}
+    # beside the CPU number: upstream's own CUDA extension on the same sample, where it was built
+    up = _upstream_on_gpu(O, c, dims, qkv, table, rpi)
+    if up is not None:
+        res["upstream_gpu"] = up
+    return res
 
 
 def _upstream_on_gpu(O, c, dims, qkv, table, rpi, reps: int = 5):
@@ -577,7 +761,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
-    ap.add_argument("--tile", type=int, default=0, help="override the rows per work item (experiments)")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (other dtype, "
+                                                               "same-scene control, window-range shard lines)")
     ap.add_argument("--workload", default="room", choices=["room", "skewed"],
                     help="room: the default line (W-MSA + SW-MSA on a 150k-voxel room); skewed: one 10^6-voxel "
                          "skewed-occupancy scene sharded by window ranges (secondary)")

@@ -162,7 +162,9 @@ int ssw_bucket_windows(const int32_t* coords, const ssw_geometry* geom,
  * (details in ssw_last_cuda_error) when L->scratch_ints exceeds
  * ssw_bucket_windows_static_capacity().  The function allocates nothing, neither through CUDA nor
  * through any library.  The first call on a device looks up the array's device address; make that
- * first call outside any stream capture.  All calls on a device share the one array and each call
+ * first call outside any stream capture.  The address is remembered per device for the life of
+ * the process, so do not call this after destroying the device's context (cudaDeviceReset).  All
+ * calls on a device share the one array and each call
  * clears the part it uses, so two calls whose kernels overlap on the GPU (different streams)
  * corrupt each other: serialise them. */
 int64_t ssw_bucket_windows_static_capacity(void);
@@ -285,6 +287,16 @@ int ssw_softmax_rows_bwd(const int32_t* row_ids, int64_t nnz, int32_t n_rows, co
  * mask[..., pos_j] (mask [mask_windows, mask_n] int8, may be NULL). */
 int ssw_coo_add_bias_mask(int dtype, const void* vals, const int32_t* idx, int64_t nnz, const void* dense, int32_t n,
                           const int8_t* mask, int32_t mask_windows, int32_t mask_n, void* out, void* stream);
+
+/* ---- debugging aid (host only) -------------------------------------------------------
+ * No counterpart in upstream (it launches on the legacy default stream and captures nothing).
+ * Writes the dependency edges of a captured CUDA graph (a cudaGraph_t) as text, one per line:
+ *   <from> -> <to> <full|programmatic> from_port=<p> to_port=<p>
+ * nodes as <index>:<name>, kernel nodes by function name, other nodes as node_type_<n>.  The launches of one call of this
+ * library are chained with programmatic dependent launch; this shows how a capture wired them and
+ * that joins between streams stayed full dependencies.  SSW_E_WORKSPACE if `text` is too small. */
+int ssw_debug_graph_edges(void* graph, char* text, int64_t text_bytes, int64_t* n_nodes, int64_t* n_edges,
+                          int64_t* n_programmatic);
 
 #ifdef __cplusplus
 }

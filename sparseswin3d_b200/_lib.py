@@ -80,6 +80,7 @@ def _load() -> C.CDLL:
         "ssw_softmax_rows_fwd": (C.c_int, [vp, i64, i32, vp, vp, vp, vp]),
         "ssw_softmax_rows_bwd": (C.c_int, [vp, i64, i32, vp, vp, vp, vp, vp]),
         "ssw_coo_add_bias_mask": (C.c_int, [C.c_int, vp, vp, i64, vp, i32, vp, i32, i32, vp, vp]),
+        "ssw_debug_graph_edges": (C.c_int, [vp, C.c_char_p, i64, P(i64), P(i64), P(i64)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)  # AttributeError here = header and library disagree
@@ -120,3 +121,18 @@ def stream_ptr(device=None) -> int:
     import torch
 
     return torch.cuda.current_stream(device).cuda_stream
+
+
+def graph_edges(graph) -> dict:
+    """Dependency edges of a captured ``torch.cuda.CUDAGraph`` (created with keep_graph=True):
+    {"nodes", "edges": [(from, to, "full" | "programmatic", from_port, to_port)], "programmatic"}."""
+    buf = C.create_string_buffer(1 << 20)
+    nn, ne, npg = i64(), i64(), i64()
+    check(lib.ssw_debug_graph_edges(graph.raw_cuda_graph(), buf, len(buf), C.byref(nn), C.byref(ne), C.byref(npg)),
+          "ssw_debug_graph_edges")
+    edges = []
+    for line in buf.value.decode().splitlines():
+        a, rest = line.split(" -> ", 1)
+        b, kind, fp, tp = rest.rsplit(" ", 3)
+        edges.append((a, b, kind, int(fp.split("=")[1]), int(tp.split("=")[1])))
+    return {"nodes": nn.value, "edges": edges, "programmatic": npg.value}

@@ -39,7 +39,12 @@ def window_attention_fused_backward(qkv: torch.Tensor, grad_out: torch.Tensor, p
 
 
 class FusedWindowAttention(torch.autograd.Function):
-    """window_attention_fused with autograd: forward keeps qkv and the table, backward recomputes."""
+    """window_attention_fused with autograd: forward keeps qkv and the table, backward recomputes.
+
+    The backward walks the same plan again.  A plan that lives in a caller-owned ``plan_buffer``
+    must therefore stay untouched until the backward has run: rebuilding another plan into that
+    buffer in between makes the backward follow a plan for other inputs (the kernels hold every
+    entry to its bounds and flag SSW_DEV_BAD_PLAN, but the gradients are then meaningless)."""
 
     @staticmethod
     def forward(ctx, qkv, table, plan, scale, use_mask):
@@ -131,6 +136,7 @@ class WindowAttentionSparse(nn.Module):
         if len(window_size) != 3:
             raise ValueError("window_size must have three entries")
         self.dim, self.window_size, self.num_heads = dim, tuple(window_size), num_heads
+        self.strict = True  # forward() raises on device-side error bits (see forward)
         head_dim = dim // num_heads
         self.scale = head_dim ** -0.5
         ws = self.window_size
@@ -191,9 +197,17 @@ class WindowAttentionSparse(nn.Module):
         x = x.replace_feature(x_.values.reshape(x.features.shape).index_select(0, arg_sort))
         return x.replace_feature(self.proj_drop(self.proj(x.features)))
 
-    def forward(self, x, mask, plan: Optional[WindowPlan] = None, fused: Optional[bool] = None):
+    def forward(self, x, mask, plan: Optional[WindowPlan] = None, fused: Optional[bool] = None,
+                strict: Optional[bool] = None):
         """The fused kernels by default (differentiable: the backward recomputes the probabilities);
-        fused=False runs upstream's operator chain on the COO surface instead."""
+        fused=False runs upstream's operator chain on the COO surface instead.
+
+        strict (default: ``self.strict``, True): after the kernels are enqueued, read the plan's
+        device-side error word back and raise on duplicate voxels, (window, pos) outside
+        [0, batch_size) x [0, n), an inconsistent plan or a device-side time-out - where upstream
+        computes garbage silently.  This is one host synchronisation per call; it is skipped while a
+        CUDA graph is being captured (check `plan.raise_on_error()` after a replay instead), and
+        callers that pass their own `plan` and want no synchronisation set strict=False."""
         if fused is None:
             fused = True
         if not fused:
@@ -201,4 +215,7 @@ class WindowAttentionSparse(nn.Module):
         if plan is None:
             with torch.no_grad():
                 plan = self.plan(x, mask, x.features.dtype)
-        return x.replace_feature(self.forward_features(x.features, plan, mask is not None))
+        y = x.replace_feature(self.forward_features(x.features, plan, mask is not None))
+        if (self.strict if strict is None else strict) and not torch.cuda.is_current_stream_capturing():
+            plan.raise_on_error()
+        return y

@@ -19,6 +19,11 @@
 //   k_attn_bwd_kv: per key row one sweep over the window's queries -> dk, dv and the bias gradient.
 // No atomics on the row gradients; the bias gradient is accumulated in a shared-memory copy of the
 // table per CTA (when it fits) and flushed with global atomics.
+//
+// The plan may be stale (the backward runs long after the forward that built it, possibly after
+// the caller rebuilt another plan in the same buffer): item counts, descriptors, voxel ids and
+// relative-position codes are held to their bounds exactly as in the forward kernels; a violation
+// sets SSW_DEV_BAD_PLAN and is replaced by a harmless value.
 #include <math.h>
 
 #include "attn_common.cuh"
@@ -31,12 +36,13 @@ struct BwdParams {
   void* dqkv;
   float* dtable;
   float* stats;  // [N * H * 4]: m (log2 domain), 1/(l + 1e-8), D, unused
-  const int32_t* header;
+  int32_t* header;
   const int4* pack_desc;
   const int32_t* pack_perm;
   const int32_t* pack_meta;
   const float* table;
   int rel_off, H, C, tile;
+  int n_vox, pack_cap;  // bounds the kernels hold the plan's voxel ids and item counts to
   float scale;
   int use_mask;
   int table_floats;  // > 0: the bias gradient is accumulated in shared memory first
@@ -126,17 +132,18 @@ __device__ __forceinline__ float score2(float qk, float qs, const float* table, 
 template <typename T, int HD>
 __global__ void __launch_bounds__(128) k_attn_bwd_q(BwdParams p) {
   const int H = p.H, C = p.C;
-  const int n_items = p.header[SSW_H_PACKS];
+  const int n_items = checked_count(p.header[SSW_H_PACKS], p);
+  const int n_small = min(checked_count(p.header[SSW_H_PACKS_SMALL], p), n_items);
   const float qs = p.scale * kLog2e;
   const T* qkv = reinterpret_cast<const T*>(p.qkv);
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-    const int4 d = __ldg(p.pack_desc + item);
+    const int4 d = checked_desc(__ldg(p.pack_desc + item), p, item < n_small);
     const int nrows = item_rows(d, p.tile);
     for (int idx = threadIdx.x; idx < nrows * H; idx += blockDim.x) {
       const int h = idx / nrows, t = idx - h * nrows;
       int row, first, c;
       if (!item_row(d, p.tile, t, row, first, c)) continue;
-      const int vi = __ldg(p.pack_perm + row), mi = __ldg(p.pack_meta + row);
+      const int vi = checked_voxel(__ldg(p.pack_perm + row), p), mi = checked_meta(__ldg(p.pack_meta + row), p);
       const int rel_i_off = meta_rel(mi) + p.rel_off;
       float q[HD], go[HD];
       load_row<T, HD>(qkv + (int64_t)vi * 3 * C + h * HD, q);
@@ -149,7 +156,8 @@ __global__ void __launch_bounds__(128) k_attn_bwd_q(BwdParams p) {
 #pragma unroll
       for (int e = 0; e < HD; ++e) dq[e] = kb[e] = 0.f;
       for (int j = 0; j < c; ++j) {
-        const int vj = __ldg(p.pack_perm + first + j), mj = __ldg(p.pack_meta + first + j);
+        const int vj = checked_voxel(__ldg(p.pack_perm + first + j), p);
+        const int mj = checked_meta(__ldg(p.pack_meta + first + j), p);
         float k[HD], v[HD];
         load_row<T, HD>(qkv + (int64_t)vj * 3 * C + C + h * HD, k);
         load_row<T, HD>(qkv + (int64_t)vj * 3 * C + 2 * C + h * HD, v);
@@ -190,24 +198,26 @@ __global__ void __launch_bounds__(128) k_attn_bwd_kv(BwdParams p) {
   for (int i = threadIdx.x; i < p.table_floats; i += blockDim.x) dtab_s[i] = 0.f;
   __syncthreads();
   grid_dependency_wait();  // the row statistics come from the kernel this one is chained behind
-  const int n_items = p.header[SSW_H_PACKS];
+  const int n_items = checked_count(p.header[SSW_H_PACKS], p);
+  const int n_small = min(checked_count(p.header[SSW_H_PACKS_SMALL], p), n_items);
   const float qs = p.scale * kLog2e;
   const T* qkv = reinterpret_cast<const T*>(p.qkv);
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-    const int4 d = __ldg(p.pack_desc + item);
+    const int4 d = checked_desc(__ldg(p.pack_desc + item), p, item < n_small);
     const int nrows = item_rows(d, p.tile);
     for (int idx = threadIdx.x; idx < nrows * H; idx += blockDim.x) {
       const int h = idx / nrows, t = idx - h * nrows;
       int row, first, c;
       if (!item_row(d, p.tile, t, row, first, c)) continue;
-      const int vj = __ldg(p.pack_perm + row), mj = __ldg(p.pack_meta + row);
+      const int vj = checked_voxel(__ldg(p.pack_perm + row), p), mj = checked_meta(__ldg(p.pack_meta + row), p);
       float k[HD], v[HD], dk[HD], dv[HD];
       load_row<T, HD>(qkv + (int64_t)vj * 3 * C + C + h * HD, k);
       load_row<T, HD>(qkv + (int64_t)vj * 3 * C + 2 * C + h * HD, v);
 #pragma unroll
       for (int e = 0; e < HD; ++e) dk[e] = dv[e] = 0.f;
       for (int i = 0; i < c; ++i) {
-        const int vi = __ldg(p.pack_perm + first + i), mi = __ldg(p.pack_meta + first + i);
+        const int vi = checked_voxel(__ldg(p.pack_perm + first + i), p);
+        const int mi = checked_meta(__ldg(p.pack_meta + first + i), p);
         float q[HD], go[HD];
         load_row<T, HD>(qkv + (int64_t)vi * 3 * C + h * HD, q);
         load_row<T, HD>(reinterpret_cast<const T*>(p.grad_out) + (int64_t)vi * C + h * HD, go);
@@ -277,7 +287,9 @@ extern "C" int ssw_attn_fused_bwd(const void* qkv, const void* grad_out, int dty
   p.dqkv = dqkv;
   p.dtable = dtable;
   p.stats = workspace;
-  p.header = plan + L->off_header;
+  p.header = const_cast<int32_t*>(plan + L->off_header);
+  p.n_vox = (int)L->n_vox;
+  p.pack_cap = (int)L->pack_cap;
   p.pack_desc = reinterpret_cast<const int4*>(plan + L->off_pack_desc);
   p.pack_perm = plan + L->off_pack_perm;
   p.pack_meta = plan + L->off_pack_meta;

@@ -30,7 +30,7 @@ struct AttnParams {
   int group_threads;  // threads of one consumer group (multiple of 32) = ceil32(tile * HG)
   int groups, stages;
   int prod_warps;     // warps that issue the row copies of an item
-  int n_vox, pack_cap;  // bounds the kernels hold the plan's voxel ids and item counts to
+  int n_vox, pack_cap, w_cap;  // bounds the kernels hold the plan's voxel ids, item and window counts to
   int split;          // CUDA-core kernel: a (row, head) is shared by two lanes, half the channels each
   float scale;
   int use_mask;
@@ -44,27 +44,60 @@ struct AttnParams {
 
 // The attention kernels turn plan entries into addresses.  A plan that is stale or was overwritten
 // must not become a wild access: entries are held to their bounds, violations set SSW_DEV_BAD_PLAN
-// and are replaced by harmless values (the output is then meaningless, and flagged).
-__device__ __forceinline__ int checked_voxel(int v, const AttnParams& p) {
-  if ((unsigned)v < (unsigned)p.n_vox) return v;
+// and are replaced by harmless values (the output is then meaningless, and flagged).  `P` is any
+// parameter block with header, n_vox, pack_cap, tile and rel_off members.
+template <typename P>
+__device__ __forceinline__ void flag_bad_plan(const P& p) {
   atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_BAD_PLAN);
+}
+template <typename P>
+__device__ __forceinline__ int checked_voxel(int v, const P& p) {
+  if ((unsigned)v < (unsigned)p.n_vox) return v;
+  flag_bad_plan(p);
   return 0;
 }
-// pack descriptor {first row, c, windows (or -(tile index)-1), window slot}
-__device__ __forceinline__ int4 checked_desc(int4 d, const AttnParams& p) {
+// pack descriptor {first row, c, windows (or -(tile index)-1), window slot}.  `want_pack`: the
+// position in the work list says which of the two forms the entry must have.
+template <typename P>
+__device__ __forceinline__ int4 checked_desc(int4 d, const P& p, bool want_pack) {
   const bool pack = d.z >= 0;
   // 32-bit arithmetic is safe here: every product is formed only after its factors are known small
-  bool ok = (unsigned)d.x < (unsigned)p.n_vox && (unsigned)(d.y - 1) < 1023u;
+  bool ok = pack == want_pack && (unsigned)d.x < (unsigned)p.n_vox && (unsigned)(d.y - 1) < 1023u && d.w >= 0;
   if (pack) ok = ok && d.z <= p.tile && d.z * d.y <= p.tile && d.z * d.y <= p.n_vox - d.x;
-  else ok = ok && d.y <= p.n_vox - d.x && -d.z - 1 <= d.y / p.tile;
+  else ok = ok && d.y > p.tile && d.y <= p.n_vox - d.x && -d.z - 1 <= (d.y - 1) / p.tile;
   if (ok) return d;
-  atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_BAD_PLAN);
-  return pack ? make_int4(0, 1, 0, 0) : make_int4(0, 1, -1, 0);  // an empty pack / a one-row window
+  flag_bad_plan(p);
+  return want_pack ? make_int4(0, 1, 0, 0) : make_int4(0, 1, -1, 0);  // an empty pack / a one-row window
 }
-__device__ __forceinline__ int checked_count(int n, const AttnParams& p) {
+template <typename P>
+__device__ __forceinline__ int checked_count(int n, const P& p) {
   if ((unsigned)n <= (unsigned)p.pack_cap) return n;
-  atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_BAD_PLAN);
+  flag_bad_plan(p);
   return 0;
+}
+// The relative-position code of a row metadata word selects a row of the bias table: codes of real
+// positions lie in [0, rel_off].
+template <typename P>
+__device__ __forceinline__ int checked_meta(int m, const P& p) {
+  if (meta_rel(m) <= p.rel_off) return m;
+  flag_bad_plan(p);
+  return m & 0xffff;
+}
+
+// First element (per head) of the COO block of the window in pack-order slot `slot` (occupancy c),
+// as an offset into the attn_vals output; the block must lie inside the sum c^2 elements the
+// caller sized that output from.  A violation is flagged and answered with -1: nothing is written.
+__device__ __forceinline__ int64_t checked_coo_block(int slot, int c, const AttnParams& p) {
+  if ((unsigned)slot < (unsigned)p.w_cap) {
+    const int kwin = __ldg(p.pack_win + slot);
+    if ((unsigned)kwin < (unsigned)p.w_cap) {
+      const unsigned start = (unsigned)__ldg(p.coo_start + kwin);
+      const unsigned total = (unsigned)p.header[SSW_H_SUMC2_LO];
+      if (p.header[SSW_H_SUMC2_HI] == 0 && start <= total && (unsigned)(c * c) <= total - start) return start;
+    }
+  }
+  flag_bad_plan(p);
+  return -1;
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -117,6 +150,25 @@ __device__ __forceinline__ bool stage_table(float* dst, const float* __restrict_
     }
   }
   return true;
+}
+
+// Bias table [rows, H] -> shared memory [rows, stride] (stride >= H, a multiple of four),
+// pre-multiplied by log2 e, pad entries zero.  Called by the first `step` threads of the CTA.
+__device__ __forceinline__ void stage_table_padded(float* dst, const float* __restrict__ src, int rows, int H, int stride,
+                                                   int tid, int step) {
+  const int n = rows * stride;
+  for (int i0 = tid; i0 < n; i0 += step * 8) {
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int i = i0 + k * step;
+      const int r = i / stride, h = i - r * stride;
+      v[k] = (i < n && h < H) ? __ldg(src + r * H + h) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (i0 + k * step < n) dst[i0 + k * step] = v[k] * kLog2e;
+  }
 }
 
 // Hardware barrier 1 over the first `n` threads of the CTA (the consumers): the producers do not

@@ -23,9 +23,9 @@
 // streamed through stage 0 without overlap; q and the output go straight through global memory.
 //
 // Every wait is a bounded poll of an mbarrier; on expiry the kernel sets SSW_DEV_TIMEOUT in the
-// plan header and every thread leaves through the same exit.
+// plan header and every thread leaves through the same exit, where the threads that issued bulk
+// copies first wait (again bounded) for the copies still in flight towards this CTA's shared memory.
 #include <math.h>
-#include <stdlib.h>
 
 #include <type_traits>
 
@@ -392,6 +392,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   const int my_items =
       n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   bool timed_out = !table_ok;
+  int issued = 0;  // producer warps: items whose row copies this warp has submitted
   if (is_producer) {
     // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
     // of item i+3 (whose descriptor arrived an iteration ago) are requested while item i is issued,
@@ -423,7 +424,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       dq[a] = a < my_items ? __ldg(p.pack_desc + item_index(a)) : make_int4(0, 0, 0, 0);
 #pragma unroll
     for (int a = 0; a < kAhead; ++a) {
-      if (a < my_items) dq[a] = checked_desc(dq[a], p);
+      if (a < my_items) dq[a] = checked_desc(dq[a], p, true);
       fetch(dq[a], vox[a], km[a]);
     }
     for (int i = 0; i < my_items; ++i) {
@@ -434,7 +435,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
                              : make_int4(0, 0, 0, 0);
       int vox_n[2], km_n[2];
       // the descriptor of item i + kAhead arrived iterations ago: checking it here waits for nothing
-      if (i + kAhead < my_items) dq[kAhead] = checked_desc(dq[kAhead], p);
+      if (i + kAhead < my_items) dq[kAhead] = checked_desc(dq[kAhead], p, true);
       fetch(dq[kAhead], vox_n, km_n);  // (an all-zero descriptor fetches nothing)
       if (use > 0 && !mbar_wait_bounded(empty + s, (use - 1) & 1)) {
         timed_out = true;
@@ -449,6 +450,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
         const int rr = (lane + 32 * k) * PW + pw;
         if (rr < nr) {
           vox[0][k] = checked_voxel(vox[0][k], p);  // loaded three items ago: no wait
+          km[0][k] = checked_meta(km[0][k], p);
           reinterpret_cast<int*>(st + kStageVoxOff)[rr] = vox[0][k];
           *reinterpret_cast<int2*>(st + kStageRowsOff + (size_t)rr * p.row_stride + data_bytes) = make_int2(
               meta_rel(km[0][k]) * H * 4, meta_region(km[0][k]) | ((meta_rel(km[0][k]) + p.rel_off) << 8));
@@ -456,6 +458,9 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       }
       // rows pw, pw + PW, ... below nr are this warp's
       const int my_rows = nr > pw ? (nr - pw + PW - 1) / PW : 0;
+      // The arrive releases the stage to the consumers: every lane's metadata stores must come
+      // before it, and the warp's copies after the byte count they complete against is announced.
+      __syncwarp();
       if (lane == 0) mbar_expect_tx(full + s, (uint32_t)my_rows * copy_bytes);
       __syncwarp();
 #pragma unroll
@@ -465,6 +470,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
           bulk_g2s(st + kStageRowsOff + (size_t)rr * p.row_stride + copy_off,
                    reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[0][k] * 3 * C, copy_bytes, full + s);
       }
+      issued = i + 1;
 #pragma unroll
       for (int a = 0; a <= kAhead; ++a) dq[a] = dq[a + 1];
       dq[kAhead + 1] = d_new;
@@ -558,24 +564,35 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
                                                   (C + h * HD) * 4, C, table_h, my_region, 0.f, (T*)nullptr);
           const float inv_l = 1.0f / (st.l + 1e-8f);  // ops.cu:164
           if (p.attn_vals) {
-            const int kwin = __ldg(p.pack_win + d.w + wl);
-            T* dst = reinterpret_cast<T*>(p.attn_vals) + ((int64_t)__ldg(p.coo_start + kwin) * H + (int64_t)h * c * c) +
-                     (int64_t)(r - kbeg) * c;
-            attend_keys_m<T, HD, true, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, kbeg, c,
-                                                   (C + h * HD) * 4, C, table_h, my_region, inv_l, dst);
+            const int64_t blk = checked_coo_block(d.w + wl, c, p);
+            T* dst = reinterpret_cast<T*>(p.attn_vals) + (blk * H + (int64_t)h * c * c) + (int64_t)(r - kbeg) * c;
+            if (blk >= 0)
+              attend_keys_m<T, HD, true, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, kbeg, c,
+                                                     (C + h * HD) * 4, C, table_h, my_region, inv_l, dst);
           }
           // Straight to global memory: each thread owns a 16-byte-aligned run of HD outputs of one
           // row (bulk stores of whole rows were tried; one bulk operation per row is what bounds them).
           store_out<T, HD>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD, st, inv_l);
         }
       }
+      // widen_rows wrote the stage through the generic proxy; the next bulk copy into it goes
+      // through the async proxy
+      if constexpr (kHalf) fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty + s);
     }
   }
   if (timed_out) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
   // A timed-out role leaves; the other roles then time out on their own bounded waits.
-  if (__syncthreads_or(timed_out)) return;
+  if (__syncthreads_or(timed_out)) {
+    // Nobody consumes what is still in flight, but the CTA must not retire under copies that
+    // target its shared memory: each producer warp waits, bounded, for the last use of every stage
+    // it submitted copies to (whether the phase completes or not, the wait outlasts any copy).
+    if (is_producer && lane == 0)
+      for (int j = max(0, issued - S); j < issued; ++j) mbar_wait_bounded(full + j % S, (j / S) & 1);
+    if (kTableSmem && threadIdx.x == 0 && !table_ok) mbar_wait_bounded(tbar, 0);
+    return;
+  }
 
   // ------------------------------------------------------------------------------------------
   // Phase B: windows with c > tile; one query tile per item, key tiles through stage 0
@@ -591,7 +608,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   uint64_t* tbars[2] = {bbar, bbar + 1};
   uint32_t tphase[2] = {0, 0};
   for (int item = n_small + blockIdx.x; item < n_items; item += gridDim.x) {
-    const int4 d = checked_desc(__ldg(p.pack_desc + item), p);
+    const int4 d = checked_desc(__ldg(p.pack_desc + item), p, false);
     const int c = d.y;
     const int q_first = (-d.z - 1) * tile;
     const int q_rows = min(tile, c - q_first);
@@ -600,7 +617,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
     if (row_active) {
       const int row = d.x + q_first + r;
       my_vox = checked_voxel(__ldg(p.pack_perm + row), p);
-      const int m = __ldg(p.pack_meta + row);
+      const int m = checked_meta(__ldg(p.pack_meta + row), p);
       my_rel = (meta_rel(m) + p.rel_off) * H;
       my_region = meta_region(m);
     }
@@ -615,7 +632,7 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       if ((int)threadIdx.x < rows_t) {
         const int row = d.x + k0 + threadIdx.x;
         const int vj = checked_voxel(__ldg(p.pack_perm + row), p);
-        const int km = __ldg(p.pack_meta + row);
+        const int km = checked_meta(__ldg(p.pack_meta + row), p);
         *reinterpret_cast<int2*>(rb + (size_t)threadIdx.x * p.row_stride + data_bytes) =
             make_int2(meta_rel(km) * H * 4, meta_region(km));
         bulk_g2s(rb + (size_t)threadIdx.x * p.row_stride + copy_off,
@@ -632,9 +649,9 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       const float* table_h = table_base + my_rel + h;
       T* emit = nullptr;
       if (n_pass == 2 && row_active) {
-        const int kwin = __ldg(p.pack_win + d.w);
-        emit = reinterpret_cast<T*>(p.attn_vals) + ((int64_t)__ldg(p.coo_start + kwin) * H + (int64_t)h * c * c) +
-               (int64_t)(q_first + r) * c;
+        const int64_t blk = checked_coo_block(d.w, c, p);
+        if (blk >= 0)
+          emit = reinterpret_cast<T*>(p.attn_vals) + (blk * H + (int64_t)h * c * c) + (int64_t)(q_first + r) * c;
       }
       issue_tile(0);
       for (int q = 0; q < n_seq; ++q) {
@@ -646,7 +663,12 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
         __syncthreads();                        // row metadata of tile q visible
         const bool ok = mbar_wait_bounded(tbars[b], tphase[b]);
         if (__syncthreads_or(!ok)) {
-          if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
+          if (threadIdx.x == 0) {
+            atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
+            // drain: this tile's copies and, if issued, the next tile's, before the CTA retires
+            mbar_wait_bounded(tbars[b], tphase[b]);
+            if (q + 1 < n_seq) mbar_wait_bounded(tbars[b ^ 1], tphase[b ^ 1]);
+          }
           return;
         }
         tphase[b] ^= 1;
@@ -668,12 +690,13 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
             if (q < n_tiles)
               attend_keys_m<T, HD, false, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, 0, rows_t,
                                                       (C + h * HD) * 4, C, table_h, my_region, 0.f, (T*)nullptr);
-            else
+            else if (emit)
               attend_keys_m<T, HD, true, kTableSmem>(p.use_mask != 0, st, rows, p.row_stride, data_bytes, 0, rows_t,
                                                      (C + h * HD) * 4, C, table_h, my_region, inv_l, emit + k0);
           }
         }
         if (q == n_tiles - 1) inv_l = 1.0f / (st.l + 1e-8f);
+        if constexpr (kHalf) fence_async_smem();  // the widened rows were written through the generic proxy
         __syncthreads();  // everyone done with this tile before it is overwritten
       }
       if (row_active)
@@ -719,21 +742,8 @@ static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, cons
   int groups = stages - 1;
   if (groups > kMaxGroups) groups = kMaxGroups;
   s.prod_warps = 2;
-  if (const char* e = getenv("SSW_PROD_WARPS")) {  // tuning override (experiments only)
-    const int v = atoi(e);
-    if (v >= 1 && v <= kMaxProducerWarps) s.prod_warps = v;
-  }
   while (groups > 1 && groups * s.group_threads + 32 * s.prod_warps > (split ? 768 : 1024)) --groups;
   if (groups < 1) groups = 1;
-  // Tuning overrides (experiments only): SSW_STAGES / SSW_GROUPS within the shared-memory budget.
-  if (const char* e = getenv("SSW_STAGES")) {
-    const int v = atoi(e);
-    if (v >= 2 && v <= stages) s.stages = stages = v;
-  }
-  if (const char* e = getenv("SSW_GROUPS")) {
-    const int v = atoi(e);
-    if (v >= 1 && v <= kMaxGroups && v <= stages && v * s.group_threads + 32 * s.prod_warps <= 1024) groups = v;
-  }
   s.groups = groups;
   s.smem = fixed + (size_t)(stages > 0 ? stages : 1) * s.stage_bytes;
   return s;
@@ -836,6 +846,7 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   p.use_mask = use_mask;
   p.n_vox = (int)L->n_vox;
   p.pack_cap = (int)L->pack_cap;
+  p.w_cap = (int)L->w_cap;
   if (L->padded) {
     // padded plan: the tensor-core kernel takes both the packs and the windows beyond a pack
     if (elt != 2 || attn_vals) return SSW_E_INVALID;
@@ -843,7 +854,6 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   }
   // fp32 without the COO output: the channels of a (row, head) are split over a lane pair
   bool split = dtype == SSW_F32 && !attn_vals && head_dim % 8 == 0;
-  if (const char* e = getenv("SSW_SPLIT")) split = split && atoi(e) != 0;  // tuning override (experiments only)
   KernelShape s = kernel_shape(tile, heads, head_dim, elt, rpb_window, split);
   if (split && s.groups * s.group_threads + 32 * s.prod_warps > 768) {
     split = false;

@@ -7,16 +7,25 @@
 //
 //   * The plan is *padded*: inside a pack every window gets a run of row slots rounded up to
 //     1, 2, 4, 8, 16, 32, 48 or 64, so a 16-slot MMA tile holds whole windows (several when c < 16)
-//     or a 16-row slice of one window.  Unused slots hold zeros or stale (finite) rows; their keys
-//     are masked out, their query rows are never stored.
-//   * A unit of work is (16-slot tile, head).  Q comes in as A fragments (ldmatrix), K as B
-//     fragments (ldmatrix), S = Q K^T lands in fp32 accumulators whose layout is also the A layout
-//     of the next MMA, so P = softmax(S) is packed to 16 bit in registers and multiplied with V
-//     (ldmatrix.trans).  Longer key ranges loop over 16-key blocks with an online softmax.
+//     or a 16-row slice of one window.  Unused slots keep whatever an earlier item left in their
+//     q and k parts (their scores are replaced, not multiplied, so the contents do not matter) and
+//     get their v part zeroed by the producer (p = 0 times a stale Inf would be NaN); their query
+//     rows are never stored.
+//   * Q comes in as A fragments (ldmatrix), K as B fragments (ldmatrix), S = Q K^T lands in fp32
+//     accumulators whose layout is also the A layout of the next MMA, so P = softmax(S) is packed
+//     to 16 bit in registers and multiplied with V (ldmatrix.trans).
+//   * Windows of up to 16 voxels (nine in ten on a surface scene): a warp takes a 16-slot tile and
+//     walks all heads inside it, so the per-key metadata, the window / region comparisons and the
+//     bias rows (one 16-byte load per (query, key) pair brings four heads) are worked out once per
+//     tile.  Larger windows: a unit of work is (16-slot tile, head) looping over 16-key blocks with
+//     an online softmax.
 //   * Softmax keeps upstream's semantics: the running maximum starts at 0, the denominator gets
-//     +1e-8; bias from the shared-memory table (pre-multiplied by log2 e), -100 shift mask.
-//   * The output tile overwrites the q slice it came from; the warp then copies it out with
-//     coalesced 16-byte stores.
+//     +1e-8; bias from the shared-memory table (pre-multiplied by log2 e, heads padded to a
+//     multiple of four), -100 shift mask.
+//   * Outputs go from the accumulator registers straight to the voxels' rows.
+//   * Values that are not finite: upstream confines them to their own window; here a v row that
+//     holds Inf or NaN also spoils the other windows that share its 16-slot tile (p = 0 for those
+//     keys, and 0 * Inf is NaN inside the MMA).
 //
 // Phase 1 (packs): every consumer group of four warps takes whole work items, one per pipeline
 // stage.  Phase 2 (windows with more voxels than a pack holds): a work item is one tile of query
@@ -24,7 +33,6 @@
 // other stages tile by tile, and all consumer warps work on the same key tile, each on its own
 // (16 query rows, head) unit whose accumulators stay in registers for the whole window.
 #include <math.h>
-#include <stdlib.h>
 
 #include "attn_common.cuh"
 
@@ -63,36 +71,167 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 // Metadata of a staged row (see kMmaRelShift): what the producer writes behind the row's data.
-__device__ __forceinline__ int2 row_meta(int m, int window, int H, int rel_off) {
-  return make_int2(meta_rel(m) * H * 4, meta_region(m) | (window << 5) | ((meta_rel(m) + rel_off) << kMmaRelShift));
+// .x: the row's relative-position code (its key-side share of a bias-table row index),
+// .y: region | window << 5 | (code + rel_off) << 12 (the query-side share).
+__device__ __forceinline__ int2 row_meta(int m, int window, int rel_off) {
+  return make_int2(meta_rel(m), meta_region(m) | (window << 5) | ((meta_rel(m) + rel_off) << kMmaRelShift));
+}
+// zero the v part (C elements from byte 2*C*sizeof(T)) of a staged row
+template <typename T>
+__device__ __forceinline__ void zero_v(unsigned char* row, int C) {
+  uint4* v = reinterpret_cast<uint4*>(row + 2 * C * sizeof(T));
+  for (int i = 0; i < (C * (int)sizeof(T)) / 16; ++i) v[i] = make_uint4(0, 0, 0, 0);
 }
 __device__ __forceinline__ int2 pad_meta(int rel_off) {
   return make_int2(0, (kMmaPadWindow << 5) | (rel_off << kMmaRelShift));
 }
 
-// One (16 query rows, head) unit: the q fragments, the two rows' metadata, the running softmax and
-// the output accumulators of this lane (rows lane/4 and lane/4 + 8 of the tile).
+// Bias of (query row meta .y, key meta .x) for head h, in the log2 domain.  `tstride`: floats per
+// table row (heads padded to a multiple of four in shared memory, the caller's H in global memory).
+template <bool kTableSmem>
+__device__ __forceinline__ float bias_of(const float* table_base, int tstride, int me_y, int km_x, int h) {
+  const float* t = table_base + ((me_y >> kMmaRelShift) - km_x) * tstride + h;
+  return kTableSmem ? *t : __ldg(t) * kLog2e;
+}
+// Additive mask of a (query, key) pair from the XOR of their metadata words: -inf across windows
+// (bits 5..11), -100 across shift-mask regions (bits 0..4), else 0.
+template <bool kMask>
+__device__ __forceinline__ float pair_mask(int x) {
+  if (x & kMmaWindowBits) return -INFINITY;
+  return (kMask && (x & 31)) ? -100.0f * kLog2e : 0.f;
+}
+
+// A 16-slot tile whose windows hold at most 16 voxels: the tile's 16 slots are also its keys.  The
+// warp walks all heads; everything that does not depend on the head is computed once.
+template <typename T, int HD, bool kTableSmem, bool kMask>
+__device__ __forceinline__ void tile_all_heads(const unsigned char* rows, int row_stride, int data_bytes, const int* svox,
+                                               int slot0, int H, int C, const float* table_base, int tstride,
+                                               float qscale, T* out, int lane) {
+  const int qr = lane >> 2, qt = lane & 3, mi = lane >> 3;
+  const unsigned char* r_lo = rows + (size_t)(slot0 + qr) * row_stride;
+  const unsigned char* r_hi = r_lo + 8 * (size_t)row_stride;
+  const int me_lo = reinterpret_cast<const int2*>(r_lo + data_bytes)->y;
+  const int me_hi = reinterpret_cast<const int2*>(r_hi + data_bytes)->y;
+  const int v_lo = svox[slot0 + qr], v_hi = svox[slot0 + qr + 8];
+  // column j of this lane: key slot n*8 + qt*2 + e with j = n*2 + e
+  float madd_lo[4], madd_hi[4];
+  int kx[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int ks = slot0 + (j >> 1) * 8 + qt * 2 + (j & 1);
+    const int2 km = *reinterpret_cast<const int2*>(rows + (size_t)ks * row_stride + data_bytes);
+    kx[j] = km.x;
+    madd_lo[j] = pair_mask<kMask>(km.y ^ me_lo);
+    madd_hi[j] = pair_mask<kMask>(km.y ^ me_hi);
+  }
+  const unsigned char* qp = rows + (size_t)(slot0 + (mi & 1) * 8 + (lane & 7)) * row_stride + (mi >> 1) * 8 * sizeof(T);
+  const unsigned char* kp = rows + (size_t)(slot0 + (mi >> 1) * 8 + (lane & 7)) * row_stride + (C + (mi & 1) * 8) * sizeof(T);
+  const unsigned char* vp = rows + (size_t)(slot0 + (mi & 1) * 8 + (lane & 7)) * row_stride + (2 * C + (mi >> 1) * 8) * sizeof(T);
+  T* o_lo = out + (int64_t)(v_lo < 0 ? 0 : v_lo) * C + qt * 2;
+  T* o_hi = out + (int64_t)(v_hi < 0 ? 0 : v_hi) * C + qt * 2;
+  for (int h0 = 0; h0 < H; h0 += 4) {
+    // biases of the lane's eight (row, column) pairs for four heads at a time
+    float4 b_lo[4], b_hi[4];
+    if constexpr (kTableSmem) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        b_lo[j] = *reinterpret_cast<const float4*>(table_base + ((me_lo >> kMmaRelShift) - kx[j]) * tstride + h0);
+        b_hi[j] = *reinterpret_cast<const float4*>(table_base + ((me_hi >> kMmaRelShift) - kx[j]) * tstride + h0);
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int h = h0 + t;
+      if (h >= H) break;
+      const int hoff = h * HD * (int)sizeof(T);
+      float sacc[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        uint32_t qf[4], kf[4];
+        ldmatrix_x4(qf, qp + hoff + ks * 16 * sizeof(T));
+        ldmatrix_x4(kf, kp + hoff + ks * 16 * sizeof(T));
+        mma16816<T>(sacc[0], qf, kf[0], kf[1]);
+        mma16816<T>(sacc[1], qf, kf[2], kf[3]);
+      }
+      float s_lo[4], s_hi[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float bl, bh;
+        if constexpr (kTableSmem) {
+          bl = t == 0 ? b_lo[j].x : t == 1 ? b_lo[j].y : t == 2 ? b_lo[j].z : b_lo[j].w;
+          bh = t == 0 ? b_hi[j].x : t == 1 ? b_hi[j].y : t == 2 ? b_hi[j].z : b_hi[j].w;
+        } else {
+          bl = bias_of<false>(table_base, tstride, me_lo, kx[j], h);
+          bh = bias_of<false>(table_base, tstride, me_hi, kx[j], h);
+        }
+        s_lo[j] = fmaf(sacc[j >> 1][j & 1], qscale, bl) + madd_lo[j];
+        s_hi[j] = fmaf(sacc[j >> 1][2 + (j & 1)], qscale, bh) + madd_hi[j];
+      }
+      // the row maximum starts from 0 (ops.cu:137)
+      float m_lo = fmaxf(fmaxf(s_lo[0], s_lo[1]), fmaxf(s_lo[2], s_lo[3]));
+      float m_hi = fmaxf(fmaxf(s_hi[0], s_hi[1]), fmaxf(s_hi[2], s_hi[3]));
+      m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
+      m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
+      m_lo = fmaxf(fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2)), 0.f);
+      m_hi = fmaxf(fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2)), 0.f);
+      float p_lo[4], p_hi[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        p_lo[j] = fast_exp2(s_lo[j] - m_lo);
+        p_hi[j] = fast_exp2(s_hi[j] - m_hi);
+      }
+      float l_lo = (p_lo[0] + p_lo[1]) + (p_lo[2] + p_lo[3]);
+      float l_hi = (p_hi[0] + p_hi[1]) + (p_hi[2] + p_hi[3]);
+      l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+      l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+      l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+      l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+      uint32_t pf[4];
+      pf[0] = pack2<T>(p_lo[0], p_lo[1]);
+      pf[1] = pack2<T>(p_hi[0], p_hi[1]);
+      pf[2] = pack2<T>(p_lo[2], p_lo[3]);
+      pf[3] = pack2<T>(p_hi[2], p_hi[3]);
+      const float inv_lo = 1.0f / (l_lo + 1e-8f), inv_hi = 1.0f / (l_hi + 1e-8f);  // ops.cu:164
+#pragma unroll
+      for (int n = 0; n < HD / 8; n += 2) {
+        uint32_t vf[4];
+        float oa[4] = {0.f, 0.f, 0.f, 0.f}, ob[4] = {0.f, 0.f, 0.f, 0.f};
+        ldmatrix_x4_trans(vf, vp + hoff + n * 8 * sizeof(T));
+        mma16816<T>(oa, pf, vf[0], vf[1]);
+        mma16816<T>(ob, pf, vf[2], vf[3]);
+        if (v_lo >= 0) {
+          *reinterpret_cast<uint32_t*>(o_lo + h * HD + n * 8) = pack2<T>(oa[0] * inv_lo, oa[1] * inv_lo);
+          *reinterpret_cast<uint32_t*>(o_lo + h * HD + n * 8 + 8) = pack2<T>(ob[0] * inv_lo, ob[1] * inv_lo);
+        }
+        if (v_hi >= 0) {
+          *reinterpret_cast<uint32_t*>(o_hi + h * HD + n * 8) = pack2<T>(oa[2] * inv_hi, oa[3] * inv_hi);
+          *reinterpret_cast<uint32_t*>(o_hi + h * HD + n * 8 + 8) = pack2<T>(ob[2] * inv_hi, ob[3] * inv_hi);
+        }
+      }
+    }
+  }
+}
+
+// One (16 query rows, head) unit of a window that spans several 16-key blocks: the q fragments, the
+// two rows' metadata, the running softmax and the output accumulators of this lane (rows lane/4 and
+// lane/4 + 8 of the tile).
 template <int HD>
 struct MmaUnit {
   uint32_t qf[HD / 16][4];
   float o[HD / 8][4];
   float m_lo, m_hi, l_lo, l_hi;
   int me_lo_y, me_hi_y;
-  const unsigned char* tab_lo;
-  const unsigned char* tab_hi;
 };
 
 // Start a unit on query slots [slot0, slot0 + 16) of the staged rows, head h.
 template <typename T, int HD>
 __device__ __forceinline__ void unit_begin(MmaUnit<HD>& u, const unsigned char* rows, int row_stride, int data_bytes,
-                                           int slot0, int h, int H, const float* table_base, int lane) {
+                                           int slot0, int h, int lane) {
   const int qr = lane >> 2, mi = lane >> 3;
-  const int2 me_lo = *reinterpret_cast<const int2*>(rows + (size_t)(slot0 + qr) * row_stride + data_bytes);
-  const int2 me_hi = *reinterpret_cast<const int2*>(rows + (size_t)(slot0 + qr + 8) * row_stride + data_bytes);
-  u.me_lo_y = me_lo.y;
-  u.me_hi_y = me_hi.y;
-  u.tab_lo = reinterpret_cast<const unsigned char*>(table_base + (me_lo.y >> kMmaRelShift) * H + h);
-  u.tab_hi = reinterpret_cast<const unsigned char*>(table_base + (me_hi.y >> kMmaRelShift) * H + h);
+  u.me_lo_y = reinterpret_cast<const int2*>(rows + (size_t)(slot0 + qr) * row_stride + data_bytes)->y;
+  u.me_hi_y = reinterpret_cast<const int2*>(rows + (size_t)(slot0 + qr + 8) * row_stride + data_bytes)->y;
   const unsigned char* qp =
       rows + (size_t)(slot0 + (mi & 1) * 8 + (lane & 7)) * row_stride + (h * HD + (mi >> 1) * 8) * sizeof(T);
 #pragma unroll
@@ -107,7 +246,8 @@ __device__ __forceinline__ void unit_begin(MmaUnit<HD>& u, const unsigned char* 
 // k_off / v_off: byte offsets of this head's k and v slices inside a staged row.
 template <typename T, int HD, bool kTableSmem, bool kMask>
 __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned char* rows, int row_stride, int data_bytes,
-                                               int ks0, int k_off, int v_off, float qscale, int lane) {
+                                               int ks0, int k_off, int v_off, const float* table_base, int tstride, int h,
+                                               float qscale, int lane) {
   const int qt = lane & 3, mi = lane >> 3;
   float sacc[2][4];
 #pragma unroll
@@ -128,19 +268,10 @@ __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned ch
     for (int e = 0; e < 2; ++e) {
       const int ks = ks0 + n * 8 + qt * 2 + e;  // key slot of this column
       const int2 km = *reinterpret_cast<const int2*>(rows + (size_t)ks * row_stride + data_bytes);
-      // one XOR per (query row, key) tells both: same window (bits 5..11), same region (bits 0..4)
-      const int x_lo = km.y ^ u.me_lo_y, x_hi = km.y ^ u.me_hi_y;
-      const bool ok_lo = (x_lo & kMmaWindowBits) == 0, ok_hi = (x_hi & kMmaWindowBits) == 0;
-      const float madd_lo = (kMask && (x_lo & 31)) ? -100.0f * kLog2e : 0.f;
-      const float madd_hi = (kMask && (x_hi & 31)) ? -100.0f * kLog2e : 0.f;
-      const float b_lo = kTableSmem ? *reinterpret_cast<const float*>(u.tab_lo - km.x)
-                                    : __ldg(reinterpret_cast<const float*>(u.tab_lo - km.x)) * kLog2e;
-      const float b_hi = kTableSmem ? *reinterpret_cast<const float*>(u.tab_hi - km.x)
-                                    : __ldg(reinterpret_cast<const float*>(u.tab_hi - km.x)) * kLog2e;
-      float s_lo = fmaf(sacc[n][e], qscale, b_lo) + madd_lo;
-      float s_hi = fmaf(sacc[n][2 + e], qscale, b_hi) + madd_hi;
-      s_lo = ok_lo ? s_lo : -INFINITY;
-      s_hi = ok_hi ? s_hi : -INFINITY;
+      const float s_lo = fmaf(sacc[n][e], qscale, bias_of<kTableSmem>(table_base, tstride, u.me_lo_y, km.x, h)) +
+                         pair_mask<kMask>(km.y ^ u.me_lo_y);
+      const float s_hi = fmaf(sacc[n][2 + e], qscale, bias_of<kTableSmem>(table_base, tstride, u.me_hi_y, km.x, h)) +
+                         pair_mask<kMask>(km.y ^ u.me_hi_y);
       sacc[n][e] = s_lo;
       sacc[n][2 + e] = s_hi;
       mx_lo = fmaxf(mx_lo, s_lo);
@@ -177,17 +308,6 @@ __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned ch
   pf[1] = pack2<T>(p02, p03);
   pf[2] = pack2<T>(p10, p11);
   pf[3] = pack2<T>(p12, p13);
-  // bf16 keeps 8 bits of a probability: too coarse for rows that sum many keys or cancel.  The
-  // rounding residual goes through a second MMA (the tensor pipe is far from busy), which leaves the
-  // output rounding as the only 16-bit step after the scores.
-  constexpr bool kSplitP = std::is_same<T, __nv_bfloat16>::value;
-  uint32_t pl[4];
-  if constexpr (kSplitP) {
-    pl[0] = pack2<T>(p00 - __uint_as_float(pf[0] << 16), p01 - __uint_as_float(pf[0] & 0xffff0000u));
-    pl[1] = pack2<T>(p02 - __uint_as_float(pf[1] << 16), p03 - __uint_as_float(pf[1] & 0xffff0000u));
-    pl[2] = pack2<T>(p10 - __uint_as_float(pf[2] << 16), p11 - __uint_as_float(pf[2] & 0xffff0000u));
-    pl[3] = pack2<T>(p12 - __uint_as_float(pf[3] << 16), p13 - __uint_as_float(pf[3] & 0xffff0000u));
-  }
   const unsigned char* vp = rows + (size_t)(ks0 + (mi & 1) * 8 + (lane & 7)) * row_stride + v_off + (mi >> 1) * 8 * sizeof(T);
 #pragma unroll
   for (int n = 0; n < HD / 8; n += 2) {
@@ -195,19 +315,15 @@ __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned ch
     ldmatrix_x4_trans(vf, vp + n * 8 * sizeof(T));
     mma16816<T>(u.o[n], pf, vf[0], vf[1]);
     mma16816<T>(u.o[n + 1], pf, vf[2], vf[3]);
-    if constexpr (kSplitP) {
-      mma16816<T>(u.o[n], pl, vf[0], vf[1]);
-      mma16816<T>(u.o[n + 1], pl, vf[2], vf[3]);
-    }
   }
 }
 
-// Normalise the unit's output, park it in the q slice the unit was read from and copy the tile's
-// 16 x HD outputs to the voxels' rows with 16-byte stores (bulk stores of whole rows were tried;
-// one bulk operation per row is what bounds them).  `svox`: voxel of every slot, -1 for unused.
+// Normalise the unit's output and store it from the accumulator registers to the voxels' rows
+// (each lane owns two adjacent channels per 8-channel block of rows lane/4 and lane/4 + 8).
+// `svox`: voxel of every slot, -1 for unused.
 template <typename T, int HD>
-__device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, unsigned char* rows, int row_stride, const int* svox,
-                                            int slot0, int h, int C, T* out, int lane) {
+__device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, const int* svox, int slot0, int h, int C, T* out,
+                                            int lane) {
   const int qr = lane >> 2, qt = lane & 3;
   // row sums live in four lanes each
   float ll = u.l_lo, lh = u.l_hi;
@@ -216,22 +332,16 @@ __device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, unsigned char*
   lh += __shfl_xor_sync(0xffffffffu, lh, 1);
   lh += __shfl_xor_sync(0xffffffffu, lh, 2);
   const float inv_lo = 1.0f / (ll + 1e-8f), inv_hi = 1.0f / (lh + 1e-8f);  // ops.cu:164
-  uint32_t* out_lo = reinterpret_cast<uint32_t*>(rows + (size_t)(slot0 + qr) * row_stride + (h * HD) * sizeof(T)) + qt;
-  uint32_t* out_hi = reinterpret_cast<uint32_t*>(rows + (size_t)(slot0 + qr + 8) * row_stride + (h * HD) * sizeof(T)) + qt;
+  const int v_lo = svox[slot0 + qr], v_hi = svox[slot0 + qr + 8];
+  if (v_lo >= 0) {
+    T* o = out + (int64_t)v_lo * C + h * HD + qt * 2;
 #pragma unroll
-  for (int n = 0; n < HD / 8; ++n) {
-    out_lo[n * 4] = pack2<T>(u.o[n][0] * inv_lo, u.o[n][1] * inv_lo);
-    out_hi[n * 4] = pack2<T>(u.o[n][2] * inv_hi, u.o[n][3] * inv_hi);
+    for (int n = 0; n < HD / 8; ++n) *reinterpret_cast<uint32_t*>(o + n * 8) = pack2<T>(u.o[n][0] * inv_lo, u.o[n][1] * inv_lo);
   }
-  __syncwarp();
-  constexpr int kChunks = HD / 8;  // 16-byte chunks per row segment
-  for (int idx = lane; idx < 16 * kChunks; idx += 32) {
-    const int rr = idx / kChunks, cc = idx - rr * kChunks;
-    const int slot = slot0 + rr;
-    const int v = svox[slot];
-    if (v >= 0)
-      *reinterpret_cast<uint4*>(out + (int64_t)v * C + h * HD + cc * 8) =
-          *reinterpret_cast<const uint4*>(rows + (size_t)slot * row_stride + (h * HD + cc * 8) * sizeof(T));
+  if (v_hi >= 0) {
+    T* o = out + (int64_t)v_hi * C + h * HD + qt * 2;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) *reinterpret_cast<uint32_t*>(o + n * 8) = pack2<T>(u.o[n][2] * inv_hi, u.o[n][3] * inv_hi);
   }
 }
 
@@ -248,9 +358,9 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   uint64_t* qempty = qfull + 1;                         // phase 2: query stage may be refilled
   uint64_t* tbar = reinterpret_cast<uint64_t*>(smem) + 30;  // bias table landed
   float* table_s = reinterpret_cast<float*>(smem + 256);
-  bool table_ok = true;
   unsigned char* stage0 = smem + 256 + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
   const float* table_base = kTableSmem ? table_s : p.table;
+  const int tstride = kTableSmem ? ((H + 3) & ~3) : H;  // floats per bias-table row
   const int gsize = kMmaGroupWarps * 32;
   const int n_cons = gsize * G;
   const int n_cons_warps = G * kMmaGroupWarps;
@@ -269,20 +379,15 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
     }
     mbar_init(qfull, PW);
     mbar_init(qempty, n_cons_warps);
-    mbar_init(tbar, 1);
     mbar_fence_init();
   }
-  // unused row slots are read as keys/values (and masked): they must hold finite numbers
-  for (int i = threadIdx.x; i < (S * p.stage_bytes) / 16; i += blockDim.x)
-    reinterpret_cast<uint4*>(stage0)[i] = make_uint4(0, 0, 0, 0);
-  fence_async_smem();  // order the zero fill before the bulk copies that will land in the same rows
   __syncthreads();
   grid_dependency_wait();
   const int n_items = checked_count(p.header[SSW_H_PACKS], p);
   const int n_small = min(checked_count(p.header[SSW_H_PACKS_SMALL], p), n_items);
   if constexpr (kTableSmem) {
     if (!is_producer) {  // the producers are already gathering the first items
-      table_ok = stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons, tbar);
+      stage_table_padded(table_s, p.table, p.table_floats / tstride, H, tstride, threadIdx.x, n_cons);
       consumer_sync(n_cons);
     }
   }
@@ -291,7 +396,8 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   // Phase 1: packs
   // ------------------------------------------------------------------------------------------
   const int my_items = n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  bool timed_out = !table_ok;
+  bool timed_out = false;
+  int issued = 0;  // producer warps: phase-1 items whose row copies this warp has submitted
   if (is_producer) {
     // slot -> row of the pack: window wl = slot / cpad, i = slot % cpad, valid if wl < nwin && i < c.
     // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
@@ -325,7 +431,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
       dq[a] = a < my_items ? __ldg(p.pack_desc + item_index(a)) : make_int4(0, 0, 0, 0);
 #pragma unroll
     for (int a = 0; a < kAhead; ++a) {
-      if (a < my_items) dq[a] = checked_desc(dq[a], p);
+      if (a < my_items) dq[a] = checked_desc(dq[a], p, true);
       fetch(dq[a], vox[a], km[a]);
     }
     for (int i = 0; i < my_items; ++i) {
@@ -336,7 +442,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
                              : make_int4(0, 0, 0, 0);
       int vox_n[2], km_n[2];
       // the descriptor of item i + kAhead arrived iterations ago: checking it here waits for nothing
-      if (i + kAhead < my_items) dq[kAhead] = checked_desc(dq[kAhead], p);
+      if (i + kAhead < my_items) dq[kAhead] = checked_desc(dq[kAhead], p, true);
       fetch(dq[kAhead], vox_n, km_n);  // (an all-zero descriptor fetches nothing)
       if (use > 0 && !mbar_wait_bounded(empty + s, (use - 1) & 1)) {
         timed_out = true;
@@ -349,15 +455,25 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
       for (int k = 0; k < 2; ++k) {
         const int slot = (lane + 32 * k) * PW + pw;
         if (slot < tile) {
-          if (vox[0][k] >= 0) vox[0][k] = checked_voxel(vox[0][k], p);  // loaded three items ago: no wait
+          if (vox[0][k] >= 0) {  // loaded three items ago: no wait
+            vox[0][k] = checked_voxel(vox[0][k], p);
+            km[0][k] = checked_meta(km[0][k], p);
+          }
           reinterpret_cast<int*>(st + kMmaStageVoxOff)[slot] = vox[0][k];
           // Unused slots form a window of their own with neutral codes, so their (discarded) scores
-          // index inside the bias table.
-          *reinterpret_cast<int2*>(st + kMmaStageRowsOff + (size_t)slot * p.row_stride + data_bytes) =
-              vox[0][k] >= 0 ? row_meta(km[0][k], km[0][k] & 1023, H, p.rel_off) : pad_meta(p.rel_off);
+          // index inside the bias table; their v part must not hold a stale Inf or NaN.
+          unsigned char* row = st + kMmaStageRowsOff + (size_t)slot * p.row_stride;
+          *reinterpret_cast<int2*>(row + data_bytes) =
+              vox[0][k] >= 0 ? row_meta(km[0][k], km[0][k] & 1023, p.rel_off) : pad_meta(p.rel_off);
+          if (vox[0][k] < 0) zero_v<T>(row, C);
         }
       }
       const int my_rows = __popc(__ballot_sync(0xffffffffu, vox[0][0] >= 0)) + __popc(__ballot_sync(0xffffffffu, vox[0][1] >= 0));
+      // Zeroed v parts were written through the generic proxy; a later item's bulk copy may land on
+      // them.  The arrive releases the stage to the consumers: every lane's stores come before it,
+      // and the warp's copies after the byte count they complete against is announced.
+      fence_async_smem();
+      __syncwarp();
       if (lane == 0) mbar_expect_tx(full + s, (uint32_t)my_rows * (uint32_t)data_bytes);
       __syncwarp();
 #pragma unroll
@@ -367,6 +483,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
           bulk_g2s(st + kMmaStageRowsOff + (size_t)slot * p.row_stride,
                    reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[0][k] * 3 * C, data_bytes, full + s);
       }
+      issued = i + 1;
 #pragma unroll
       for (int a = 0; a <= kAhead; ++a) dq[a] = dq[a + 1];
       dq[kAhead + 1] = d_new;
@@ -401,19 +518,24 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
       const int c = d.y, nwin = d.z;
       const int cpad = slots_of_window(c, 1);
       const int n_mt = (nwin * cpad + 15) >> 4;
-      const int nkb = cpad > 16 ? cpad >> 4 : 1;  // 16-key blocks per window
-      for (int un = wg; un < n_mt * H; un += kMmaGroupWarps) {
-        const int mt = un / H, h = un - mt * H;
-        // first key slot of the window(s) this tile belongs to
-        const int kbase = cpad > 16 ? (mt * 16 / cpad) * cpad : mt * 16;
-        MmaUnit<HD> u;
-        unit_begin<T, HD>(u, rows, p.row_stride, data_bytes, mt * 16, h, H, table_base, lane);
-        for (int kb = 0; kb < nkb; ++kb)
-          unit_key_block<T, HD, kTableSmem, kMask>(u, rows, p.row_stride, data_bytes, kbase + kb * 16,
-                                                   (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
-                                                   qscale, lane);
-        __syncwarp();
-        unit_finish<T, HD>(u, rows, p.row_stride, svox, mt * 16, h, C, reinterpret_cast<T*>(p.out), lane);
+      if (cpad <= 16) {
+        // windows of at most 16 voxels: a tile's slots are its keys; one warp per tile, all heads
+        for (int mt = wg; mt < n_mt; mt += kMmaGroupWarps)
+          tile_all_heads<T, HD, kTableSmem, kMask>(rows, p.row_stride, data_bytes, svox, mt * 16, H, C, table_base,
+                                                   tstride, qscale, reinterpret_cast<T*>(p.out), lane);
+      } else {
+        const int nkb = cpad >> 4;  // 16-key blocks per window
+        for (int un = wg; un < n_mt * H; un += kMmaGroupWarps) {
+          const int mt = un / H, h = un - mt * H;
+          const int kbase = (mt * 16 / cpad) * cpad;  // first key slot of the window this tile belongs to
+          MmaUnit<HD> u;
+          unit_begin<T, HD>(u, rows, p.row_stride, data_bytes, mt * 16, h, lane);
+          for (int kb = 0; kb < nkb; ++kb)
+            unit_key_block<T, HD, kTableSmem, kMask>(u, rows, p.row_stride, data_bytes, kbase + kb * 16,
+                                                     (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
+                                                     table_base, tstride, h, qscale, lane);
+          unit_finish<T, HD>(u, svox, mt * 16, h, C, reinterpret_cast<T*>(p.out), lane);
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty + s);
@@ -421,7 +543,14 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   }
   if (timed_out) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
   // A timed-out role leaves; the other roles then time out on their own bounded waits.
-  if (__syncthreads_or(timed_out)) return;
+  if (__syncthreads_or(timed_out)) {
+    // Nobody consumes what is still in flight, but the CTA must not retire under copies that
+    // target its shared memory: each producer warp waits, bounded, for the last use of every stage
+    // it submitted copies to (whether the phase completes or not, the wait outlasts any copy).
+    if (is_producer && lane == 0)
+      for (int j = max(0, issued - S); j < issued; ++j) mbar_wait_bounded(full + j % S, (j / S) & 1);
+    return;
+  }
   if (n_items <= n_small) return;
 
   // ------------------------------------------------------------------------------------------
@@ -436,8 +565,9 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   unsigned char* q_stage = stage0;
   unsigned char* q_rows = q_stage + kMmaStageRowsOff;
   int kseq = 0, qseq = 0;  // key tiles / query tiles handled so far by this CTA
+  int q_issued = 0, k_issued = 0;  // producer warps: query / key tiles whose copies this warp has submitted
   for (int item = n_small + blockIdx.x; item < n_items && !timed_out; item += gridDim.x, ++qseq) {
-    const int4 d = checked_desc(__ldg(p.pack_desc + item), p);
+    const int4 d = checked_desc(__ldg(p.pack_desc + item), p, false);
     const int c = d.y;
     const int q_first = (-d.z - 1) * tile;
     const int n_q = min(tile, c - q_first);
@@ -452,7 +582,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
         qm[k] = 0;
         if (slot < n_q) {
           qv[k] = checked_voxel(__ldg(p.pack_perm + d.x + q_first + slot), p);
-          qm[k] = __ldg(p.pack_meta + d.x + q_first + slot);
+          qm[k] = checked_meta(__ldg(p.pack_meta + d.x + q_first + slot), p);
         }
       }
       if (qseq > 0 && !mbar_wait_bounded(qempty, (qseq - 1) & 1)) {
@@ -465,11 +595,12 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
         if (slot < tile) {
           reinterpret_cast<int*>(q_stage + kMmaStageVoxOff)[slot] = qv[k];
           *reinterpret_cast<int2*>(q_rows + (size_t)slot * p.row_stride + data_bytes) =
-              qv[k] >= 0 ? row_meta(qm[k], 0, H, p.rel_off) : pad_meta(p.rel_off);
+              qv[k] >= 0 ? row_meta(qm[k], 0, p.rel_off) : pad_meta(p.rel_off);
         }
       }
       {
         const int my_rows = __popc(__ballot_sync(0xffffffffu, qv[0] >= 0)) + __popc(__ballot_sync(0xffffffffu, qv[1] >= 0));
+        __syncwarp();  // every lane's metadata stores before the arrive that releases them
         if (lane == 0) mbar_expect_tx(qfull, (uint32_t)my_rows * q_bytes);
         __syncwarp();
       }
@@ -480,6 +611,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
           bulk_g2s(q_rows + (size_t)slot * p.row_stride, reinterpret_cast<const T*>(p.qkv) + (int64_t)qv[k] * 3 * C,
                    q_bytes, qfull);
       }
+      q_issued = qseq + 1;
       // key tiles, once per round of heads
       for (int rt = 0; rt < rounds * n_kt && !timed_out; ++rt, ++kseq) {
         const int kt = rt % n_kt;
@@ -492,7 +624,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
           kmeta[k] = 0;
           if (slot < n_k) {
             kv[k] = checked_voxel(__ldg(p.pack_perm + d.x + k0 + slot), p);
-            kmeta[k] = __ldg(p.pack_meta + d.x + k0 + slot);
+            kmeta[k] = checked_meta(__ldg(p.pack_meta + d.x + k0 + slot), p);
           }
         }
         const int s = 1 + kseq % R, use = kseq / R;
@@ -504,11 +636,16 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const int slot = (lane + 32 * k) * PW + pw;
-          if (slot < tile)
-            *reinterpret_cast<int2*>(krows + (size_t)slot * p.row_stride + data_bytes) =
-                kv[k] >= 0 ? row_meta(kmeta[k], 0, H, p.rel_off) : pad_meta(p.rel_off);
+          if (slot < tile) {
+            unsigned char* row = krows + (size_t)slot * p.row_stride;
+            *reinterpret_cast<int2*>(row + data_bytes) =
+                kv[k] >= 0 ? row_meta(kmeta[k], 0, p.rel_off) : pad_meta(p.rel_off);
+            if (kv[k] < 0) zero_v<T>(row, C);  // p = 0 times a stale Inf would be NaN
+          }
         }
         const int my_rows = __popc(__ballot_sync(0xffffffffu, kv[0] >= 0)) + __popc(__ballot_sync(0xffffffffu, kv[1] >= 0));
+        fence_async_smem();  // the zeroed v parts (generic proxy) against later bulk copies onto them
+        __syncwarp();        // every lane's stores before the arrive that releases them
         if (lane == 0) mbar_expect_tx(dfull + s, (uint32_t)my_rows * kv_bytes);
         __syncwarp();
 #pragma unroll
@@ -518,6 +655,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
             bulk_g2s(krows + (size_t)slot * p.row_stride + q_bytes,
                      reinterpret_cast<const T*>(p.qkv) + (int64_t)kv[k] * 3 * C + C, kv_bytes, dfull + s);
         }
+        k_issued = kseq + 1;
       }
     } else {
       const int cw = threadIdx.x >> 5;  // consumer warp
@@ -530,7 +668,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
         const int h = r * heads_per_round + hsel;
         const bool active = hsel < heads_per_round && h < H && mt * 16 < n_q;
         MmaUnit<HD> u;
-        if (active) unit_begin<T, HD>(u, q_rows, p.row_stride, data_bytes, mt * 16, h, H, table_base, lane);
+        if (active) unit_begin<T, HD>(u, q_rows, p.row_stride, data_bytes, mt * 16, h, lane);
         for (int kt = 0; kt < n_kt; ++kt, ++kseq) {
           const int s = 1 + kseq % R, use = kseq / R;
           if (!mbar_wait_bounded(dfull + s, use & 1)) {
@@ -543,23 +681,25 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
             for (int kb = 0; kb * 16 < n_k; ++kb)
               unit_key_block<T, HD, kTableSmem, kMask>(u, krows, p.row_stride, data_bytes, kb * 16,
                                                        (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
-                                                       qscale, lane);
+                                                       table_base, tstride, h, qscale, lane);
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(dempty + s);
         }
-        if (active && !timed_out) {
-          __syncwarp();
-          unit_finish<T, HD>(u, q_rows, p.row_stride, reinterpret_cast<const int*>(q_stage + kMmaStageVoxOff), mt * 16, h,
-                             C, reinterpret_cast<T*>(p.out), lane);
-        }
+        if (active && !timed_out)
+          unit_finish<T, HD>(u, reinterpret_cast<const int*>(q_stage + kMmaStageVoxOff), mt * 16, h, C,
+                             reinterpret_cast<T*>(p.out), lane);
       }
       __syncwarp();
       if (lane == 0 && !timed_out) mbar_arrive(qempty);
     }
   }
   if (timed_out) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_TIMEOUT);
-  __syncthreads();
+  if (__syncthreads_or(timed_out) && is_producer && lane == 0) {
+    // drain what this warp submitted and nobody will consume (bounded, see phase 1)
+    if (q_issued > 0) mbar_wait_bounded(qfull, (q_issued - 1) & 1);
+    for (int j = max(0, k_issued - R); j < k_issued; ++j) mbar_wait_bounded(dfull + 1 + j % R, (j / R) & 1);
+  }
 }
 
 struct MmaShape {
@@ -571,7 +711,9 @@ static MmaShape mma_shape(int tile, int heads, int head_dim, const int32_t rpb_w
   const int C = heads * head_dim;
   s.row_stride = 3 * C * 2 + 16;  // +16 B: per-row metadata, and consecutive rows fall on different banks
   s.stage_bytes = kMmaStageRowsOff + tile * s.row_stride;
-  const int tf = (2 * rpb_window[0] - 1) * (2 * rpb_window[1] - 1) * (2 * rpb_window[2] - 1) * heads;
+  // in shared memory the table's rows are padded to a multiple of four heads (one 16-byte load
+  // then brings the biases of four heads)
+  const int tf = (2 * rpb_window[0] - 1) * (2 * rpb_window[1] - 1) * (2 * rpb_window[2] - 1) * ((heads + 3) & ~3);
   // The bias table goes to shared memory when four stages still fit beside it (look-ups from global
   // memory cost a dense window about a quarter of its time); otherwise it stays in global memory.
   const size_t budget = size_t(226) * 1024;
@@ -584,14 +726,6 @@ static MmaShape mma_shape(int tile, int heads, int head_dim, const int32_t rpb_w
   int groups = stages - 1;
   if (groups > kMaxGroups) groups = kMaxGroups;
   if (groups < 1) groups = 1;
-  if (const char* e = getenv("SSW_STAGES")) {  // tuning overrides (experiments only)
-    const int v = atoi(e);
-    if (v >= 3 && v <= stages) stages = v;
-  }
-  if (const char* e = getenv("SSW_GROUPS")) {
-    const int v = atoi(e);
-    if (v >= 1 && v <= kMaxGroups && v <= stages) groups = v;
-  }
   if (groups > stages) groups = stages;
   s.stages = stages;
   s.groups = groups;
@@ -613,10 +747,6 @@ static int launch_mma(AttnParams p, const MmaShape& s, cudaStream_t stream) {
   SSW_CUDA_TRY(cudaGetDevice(&dev));
   SSW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   p.prod_warps = 4;  // 16-bit rows are short: the copy submission rate, not the bytes, bounds the producer
-  if (const char* e = getenv("SSW_PROD_WARPS")) {  // tuning override (experiments only)
-    const int v = atoi(e);
-    if (v >= 1 && v <= kMaxProducerWarps) p.prod_warps = v;
-  }
   const int threads = p.groups * kMmaGroupWarps * 32 + 32 * p.prod_warps;
   // four variants: bias table in shared memory or not, shift mask or not
   void (*kern)(AttnParams) =
@@ -624,6 +754,7 @@ static int launch_mma(AttnParams p, const MmaShape& s, cudaStream_t stream) {
                          : (p.use_mask ? k_attn_mma<T, HD, false, true> : k_attn_mma<T, HD, false, false>);
   SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s.smem));
   SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), s.smem, stream, p));
+  SSW_LAUNCH_CHECK("k_attn_mma");
   return SSW_OK;
 }
 

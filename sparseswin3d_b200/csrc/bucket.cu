@@ -191,7 +191,8 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
                                                           int32_t* __restrict__ header, int32_t* __restrict__ win_id,
                                                           int32_t* __restrict__ win_start,
                                                           int32_t* __restrict__ coo_start, int32_t* __restrict__ bins_base,
-                                                          int n_per_window, int tile, int padded, int n_blocks) {
+                                                          int n_per_window, int tile, int padded, int n_blocks,
+                                                          int pack_cap) {
   extern __shared__ int32_t hist[];  // n_per_window + 2
   BinTables bins(bins_base, n_per_window);
   for (int i = threadIdx.x; i < n_per_window + 2; i += blockDim.x) hist[i] = 0;
@@ -273,11 +274,18 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
     }
     carry = tri_add(carry, tot2);
   }
+  __syncthreads();  // PACKS_SMALL (written by whichever thread owns c = tile + 1) before thread 0 may clear it
   if (threadIdx.x == 0) {
     win_start[W] = N;
     coo_start[W] = (int)sq;
-    header[SSW_H_PACKS] = (int)carry.sq;
-    if (tile + 1 > n_per_window + 1) header[SSW_H_PACKS_SMALL] = (int)carry.sq;
+    // The descriptor array holds pack_cap items (an upper bound for every occupancy histogram the
+    // layout call could foresee).  Should a count ever exceed it, the plan is declared empty and
+    // flagged rather than written past its end.
+    const bool fits = carry.sq <= (unsigned long long)pack_cap;
+    if (!fits) atomicOr(reinterpret_cast<unsigned*>(header + SSW_H_ERROR), SSW_DEV_BAD_PLAN);
+    header[SSW_H_PACKS] = fits ? (int)carry.sq : 0;
+    if (!fits) header[SSW_H_PACKS_SMALL] = 0;
+    else if (tile + 1 > n_per_window + 1) header[SSW_H_PACKS_SMALL] = (int)carry.sq;
     header[SSW_H_TILE] = tile;
     header[SSW_H_PADDED] = padded;
     if (sq >= (1ull << 31)) atomicOr(reinterpret_cast<unsigned*>(header + SSW_H_ERROR), SSW_DEV_COO_RANGE);
@@ -289,7 +297,7 @@ __global__ void __launch_bounds__(kScanThreads) k_compact(int32_t* __restrict__ 
 __global__ void k_order(const int32_t* __restrict__ header, const int32_t* __restrict__ win_start,
                         int32_t* __restrict__ win_pstart, int32_t* __restrict__ pack_win,
                         int32_t* __restrict__ pack_desc, int32_t* __restrict__ bins_base, int n_per_window, int tile,
-                        int padded, int w_blocks) {
+                        int padded, int w_blocks, int pack_cap) {
   BinTables bins(bins_base, n_per_window);
   grid_dependency_wait();
   if ((int)blockIdx.x < w_blocks) {
@@ -302,7 +310,7 @@ __global__ void k_order(const int32_t* __restrict__ header, const int32_t* __res
     return;
   }
   int p = (blockIdx.x - w_blocks) * blockDim.x + threadIdx.x;
-  if (p >= header[SSW_H_PACKS]) return;
+  if (p >= header[SSW_H_PACKS] || p >= pack_cap) return;
   // largest c with packstart[c] <= p and a non-empty bin: binary search on the monotone table
   int lo = 1, hi = n_per_window;
   while (lo < hi) {
@@ -442,7 +450,11 @@ extern "C" int ssw_plan_layout_init(ssw_plan_layout* L, int64_t n_vox, int32_t n
   L->padded = padded ? 1 : 0;
   L->w_cap = (int32_t)(n_vox < n_windows ? n_vox : n_windows);
   if (L->w_cap < 1) L->w_cap = 1;
-  int64_t pack_cap = 2 * ceil_div64(n_vox, tile_rows) + n_per_window + 2;
+  // Work items: a bin of cnt windows with occupancy c gives ceil(cnt / floor(tile / slots(c))) packs
+  // (c <= tile) or cnt * ceil(c / tile) query tiles.  With floor(x) >= x / 2 for x >= 1 and
+  // slots(c) = c (contiguous) or < 2c (padded) the sum over bins stays below
+  // (2 or 4) * N / tile + one item of rounding per occupancy.
+  int64_t pack_cap = (padded ? 4 : 2) * ceil_div64(n_vox, tile_rows) + n_per_window + 2;
   if (pack_cap >= (int64_t(1) << 31)) return SSW_E_RANGE;
   L->pack_cap = (int32_t)pack_cap;
   L->bitmap_words = (n_per_window + 31) / 32;
@@ -510,13 +522,13 @@ extern "C" int ssw_bucket_windows(const int32_t* coords, const ssw_geometry* geo
   SSW_CUDA_TRY(launch_chained(k_compact, dim3(blocks), dim3(kScanThreads), sizeof(int32_t) * (n + 2), stream, count,
                               (int)L->n_windows, (const int32_t*)partials, header, plan + L->off_win_id,
                               plan + L->off_win_start, plan + L->off_coo_start, plan + L->off_bins, n,
-                              (int)L->tile_rows, (int)L->padded, blocks));
+                              (int)L->tile_rows, (int)L->padded, blocks, (int)L->pack_cap));
   const int w_blocks = (int)ceil_div64(L->w_cap, 256);
   const int p_blocks = (int)ceil_div64(L->pack_cap, 256);
   SSW_CUDA_TRY(launch_chained(k_order, dim3(w_blocks + p_blocks), dim3(256), 0, stream, (const int32_t*)header,
                               (const int32_t*)(plan + L->off_win_start), plan + L->off_win_pstart,
                               plan + L->off_pack_win, plan + L->off_pack_desc, plan + L->off_bins, n,
-                              (int)L->tile_rows, (int)L->padded, w_blocks));
+                              (int)L->tile_rows, (int)L->padded, w_blocks, (int)L->pack_cap));
   SSW_CUDA_TRY(launch_chained(k_scatter, dim3(vox_blocks), dim3(256), 0, stream, s, N, (int)L->bitmap_words,
                               (const int32_t*)count, (const uint32_t*)bitmap, (const int32_t*)(plan + L->off_win_start),
                               (const int32_t*)(plan + L->off_win_pstart), plan + L->off_perm, plan + L->off_inv_perm,
@@ -537,7 +549,9 @@ constexpr int64_t kStaticScratchInts = int64_t(4) << 20;
 static __device__ __align__(256) int32_t g_static_scratch[kStaticScratchInts];
 
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address; the
-// address a kernel can use has to be asked for, once per device, with that device current.
+// address a kernel can use has to be asked for, once per device, with that device current.  The
+// answer is cached per device for the life of the process: a caller that destroys the device's
+// context (cudaDeviceReset) invalidates it and must not use this entry point afterwards.
 static int32_t* g_static_scratch_ptr[64] = {nullptr};
 
 extern "C" int64_t ssw_bucket_windows_static_capacity(void) { return kStaticScratchInts; }

@@ -27,3 +27,79 @@ extern "C" const char* ssw_status_string(int status) {
 extern "C" const char* ssw_last_cuda_error(void) { return ssw::g_cuda_error; }
 
 extern "C" int ssw_version(void) { return 100; }
+
+// Host-side debug helper: the dependency edges of a captured CUDA graph as text, one edge per line,
+//   <from> -> <to> <full|programmatic> from_port=<p> to_port=<p>
+// with nodes written as <index>:<name>, kernel nodes named by their function and other nodes by
+// their type number.  Lets a caller
+// check how a captured sequence of this library's chained launches was wired (which edges became
+// programmatic, and that a cross-stream join is a full dependency).  Touches no device memory.
+static void node_name(cudaGraphNode_t n, char* out, size_t cap) {
+  cudaGraphNodeType t;
+  if (cudaGraphNodeGetType(n, &t) != cudaSuccess) {
+    snprintf(out, cap, "?");
+    return;
+  }
+  if (t == cudaGraphNodeTypeKernel) {
+    cudaKernelNodeParams kp;
+    const char* name = nullptr;
+    if (cudaGraphKernelNodeGetParams(n, &kp) == cudaSuccess && kp.func && cudaFuncGetName(&name, kp.func) == cudaSuccess &&
+        name) {
+      snprintf(out, cap, "%s", name);
+      return;
+    }
+    snprintf(out, cap, "kernel");
+    return;
+  }
+  snprintf(out, cap, "node_type_%d", (int)t);
+}
+
+extern "C" int ssw_debug_graph_edges(void* graph_, char* text, int64_t text_bytes, int64_t* n_nodes, int64_t* n_edges,
+                                     int64_t* n_programmatic) {
+  cudaGraph_t graph = (cudaGraph_t)graph_;
+  if (!graph || !text || text_bytes < 1) return SSW_E_INVALID;
+  size_t nn = 0, ne = 0;
+  SSW_CUDA_TRY(cudaGraphGetNodes(graph, nullptr, &nn));
+  SSW_CUDA_TRY(cudaGraphGetEdges_v2(graph, nullptr, nullptr, nullptr, &ne));
+  cudaGraphNode_t* nodes = new cudaGraphNode_t[nn + 1];
+  if (nn > 0 && cudaGraphGetNodes(graph, nodes, &nn) != cudaSuccess) nn = 0;
+  auto index_of = [&](cudaGraphNode_t n) {
+    for (size_t i = 0; i < nn; ++i)
+      if (nodes[i] == n) return (int)i;
+    return -1;
+  };
+  cudaGraphNode_t* from = new cudaGraphNode_t[ne + 1];
+  cudaGraphNode_t* to = new cudaGraphNode_t[ne + 1];
+  cudaGraphEdgeData* ed = new cudaGraphEdgeData[ne + 1];
+  int status = SSW_OK;
+  int64_t prog = 0, pos = 0;
+  text[0] = 0;
+  if (ne > 0 && cudaGraphGetEdges_v2(graph, from, to, ed, &ne) != cudaSuccess) {
+    ssw::set_cuda_error(cudaGetLastError(), "cudaGraphGetEdges_v2");
+    status = SSW_E_CUDA;
+  } else {
+    for (size_t i = 0; i < ne; ++i) {
+      char a[200], b[200];
+      node_name(from[i], a, sizeof(a));
+      node_name(to[i], b, sizeof(b));
+      const bool p = ed[i].type == cudaGraphDependencyTypeProgrammatic;
+      prog += p;
+      const int w = snprintf(text + pos, (size_t)(text_bytes - pos), "%d:%s -> %d:%s %s from_port=%d to_port=%d\n",
+                             index_of(from[i]), a, index_of(to[i]), b, p ? "programmatic" : "full", (int)ed[i].from_port,
+                             (int)ed[i].to_port);
+      if (w < 0 || pos + w >= text_bytes) {
+        status = SSW_E_WORKSPACE;
+        break;
+      }
+      pos += w;
+    }
+  }
+  delete[] nodes;
+  delete[] from;
+  delete[] to;
+  delete[] ed;
+  if (n_nodes) *n_nodes = (int64_t)nn;
+  if (n_edges) *n_edges = (int64_t)ne;
+  if (n_programmatic) *n_programmatic = prog;
+  return status;
+}

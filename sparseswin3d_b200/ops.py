@@ -14,6 +14,9 @@ from . import _lib
 from ._lib import PlanLayout, SswError, check, dtype_code, lib, ptr, stream_ptr
 
 I32 = torch.int32
+# qkv_sparse_indices raises on duplicate / out-of-range indices (one host read-back); set to False
+# to skip the check, e.g. to keep that call free of synchronisation.
+STRICT = True
 
 
 def _ws(nbytes: int, device) -> torch.Tensor:
@@ -112,6 +115,11 @@ def qkv_sparse_indices(indices: torch.Tensor, batch_size: int, spatial_dim: int,
     plan = bucket_windows(indices=indices, n_windows=int(batch_size), n_per_window=int(spatial_dim))
     check(lib.ssw_qkv_sparse_indices(ptr(indices), N, int(num_heads), int(c), plan.layout, ptr(plan.plan), ptr(iqv),
                                      ptr(pqv), ptr(ik), ptr(pk), stream_ptr(dev)), "qkv_sparse_indices")
+    # Upstream silently mis-sorts on duplicate or out-of-range (window, pos); this operator chain
+    # synchronises a few calls later anyway (matmul_cuda_naive reads its block counts back), so the
+    # device-side error word is read here, unless a CUDA graph is being captured.
+    if STRICT and not torch.cuda.is_current_stream_capturing():
+        plan.raise_on_error()
     return iqv, pqv, ik, pk
 
 

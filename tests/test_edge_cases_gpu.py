@@ -90,21 +90,77 @@ def test_batch_of_scenes_with_full_and_singleton_windows(dtype, tol):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_overwritten_plan_is_flagged_not_followed(dtype):
-    """A plan buffer whose voxel ids were overwritten (a stale or recycled buffer): the attention
-    kernel must not use them as addresses; it sets SSW_DEV_BAD_PLAN and finishes."""
+@pytest.mark.parametrize("what", ["voxel ids", "descriptors", "item count"])
+def test_overwritten_plan_is_flagged_not_followed(dtype, what):
+    """A plan buffer that was overwritten (a stale or recycled buffer): the attention kernels, forward
+    and backward, must not turn its entries into addresses; they set SSW_DEV_BAD_PLAN and finish.
+
+    The test is built so that even a missed check stays inside memory this process owns: qkv, out
+    and the gradients are views into the middle third of allocations three times their size, and the
+    bad voxel ids are only a little outside [0, N) (within one N on either side)."""
     from sparseswin3d_b200 import _lib, attention, window
 
     dev = torch.device("cuda:0")
-    case = make_case(n_vox=1200, grid=24, seed=8)
+    N = 1200
+    case = make_case(n_vox=N, grid=24, seed=8)
     geom = window.resolve_geometry(1, case["dims"], case["window"], case["shift"])
     plan = window.bucket_windows(coords=case["coords"].to(dev), geom=geom, **attention.plan_params(3, 32, dtype))
     assert plan.stats()["error"] == 0
-    plan.pack_perm[::7] = 2 ** 30          # far outside [0, N)
-    plan.pack_perm[3::11] = -5
-    out = attention.window_attention_fused(case["qkv"].to(dtype).to(dev), plan, case["table"].to(dev), case["scale"])
+
+    def middle(rows_shape):
+        big = torch.zeros((3 * N,) + rows_shape, dtype=dtype, device=dev)
+        return big, big[N:2 * N]
+
+    qkv_big, qkv = middle((3, 3, 32))
+    qkv.copy_(case["qkv"].to(dtype))
+    out_big, out = middle((96,))
+    if what == "voxel ids":
+        plan.pack_perm[::7] = N + 17           # just beyond [0, N): lands in the upper third if followed
+        plan.pack_perm[3::11] = -5             # just below: lands in the lower third if followed
+    elif what == "descriptors":
+        d = plan.pack_desc
+        d[::5, 0] = N + 3                      # first row beyond the voxel count
+        d[1::5, 1] = 2000                      # occupancy beyond any window
+        d[2::5, 2] = 70                        # more windows than a pack holds
+    else:
+        plan.header[_lib.H_PACKS] = plan.layout.pack_cap + 1000
+    res = attention.window_attention_fused(qkv, plan, case["table"].to(dev), case["scale"], out=out)
     torch.cuda.synchronize()
-    assert out.shape == (1200, 96)
+    assert res.shape == (N, 96)
     assert plan.stats()["error"] & _lib.DEV_BAD_PLAN
+    assert float(out_big[:N].abs().sum()) == 0.0 and float(out_big[2 * N:].abs().sum()) == 0.0  # nothing written outside
     with pytest.raises(_lib.SswError):
         plan.raise_on_error()
+    # the backward follows the same plan long after the forward: same checks
+    plan.header[_lib.H_ERROR] = 0
+    go_big, go = middle((96,))
+    go.fill_(0.01)
+    dqkv, dtable = attention.window_attention_fused_backward(qkv, go, plan, case["table"].to(dev), case["scale"])
+    torch.cuda.synchronize()
+    assert dqkv.shape == qkv.shape
+    assert plan.stats()["error"] & _lib.DEV_BAD_PLAN
+
+
+def test_module_forward_raises_on_bad_indices_unless_told_not_to():
+    """Upstream computes garbage silently on duplicate (window, pos) pairs; the module raises (one
+    read-back of the plan's error word), and stays silent with strict=False."""
+    from sparseswin3d_b200 import _lib, ops
+    from sparseswin3d_b200.attention import WindowAttentionSparse
+    from sparseswin3d_b200.voxels import WindowedVoxels
+
+    dev = torch.device("cuda:0")
+    case = make_case(n_vox=400, grid=20, seed=4)
+    idx = case["indices"].clone()
+    idx[9] = idx[2]                                   # two voxels in one cell
+    m = WindowAttentionSparse(96, 3, (7, 7, 7)).to(dev)
+    x = WindowedVoxels(torch.randn(400, 96, device=dev), idx.to(dev), case["n_windows"], (case["n"],))
+    with torch.no_grad():
+        with pytest.raises(_lib.SswError):
+            m(x, None)
+        y = m(x, None, strict=False)
+        assert y.features.shape == (400, 96)
+        with pytest.raises(_lib.SswError):           # the operator surface checks as well
+            ops.qkv_sparse_indices(idx.to(dev), case["n_windows"], case["n"], 3, 32)
+        idx[9, 0] = case["n_windows"]                 # a window id beyond batch_size
+        with pytest.raises(_lib.SswError):
+            m(WindowedVoxels(x.features, idx.to(dev), case["n_windows"], (case["n"],)), None)

@@ -15,7 +15,7 @@ from tests.cases import make_case
 pytestmark = pytest.mark.gpu
 
 
-def _run_static(case, dev, tile, shift):
+def _run_static(case, dev, tile, shift, plan=None):
     from sparseswin3d_b200 import _lib
     from sparseswin3d_b200 import window as W
 
@@ -24,7 +24,8 @@ def _run_static(case, dev, tile, shift):
     L = _lib.PlanLayout()
     _lib.check(_lib.lib.ssw_plan_layout_init(L, coords.shape[0], geom.n_windows, geom.n_per_window, tile, 0), "layout")
     assert L.scratch_ints <= _lib.lib.ssw_bucket_windows_static_capacity()
-    plan = torch.empty(L.plan_ints, dtype=torch.int32, device=dev)  # the caller's output buffer
+    if plan is None:
+        plan = torch.empty(L.plan_ints, dtype=torch.int32, device=dev)  # the caller's output buffer
     rw = (_lib.i32 * 3)(*case["window"])
     rc = _lib.lib.ssw_bucket_windows_static(coords.data_ptr(), geom, None, None, 0, rw, L, plan.data_ptr(),
                                             torch.cuda.current_stream(dev).cuda_stream)
@@ -42,6 +43,17 @@ def test_static_scratch_matches_regular_entry_point_twice():
     for seed, n_vox, shift in ((31, 3000, (0, 0, 0)), (32, 1800, (3, 3, 3))):
         case = make_case(n_vox=n_vox, grid=40, shift=shift, seed=seed)
         got, geom = _run_static(case, dev, tile, shift)
+        # "allocates nothing": once its set-up call is behind it, a call leaves the device's free
+        # memory exactly where it was (every tensor the second call touches exists before the reading)
+        coords_dev = case["coords"].to(dev)
+        case_dev = dict(case, coords=coords_dev)
+        plan2 = torch.empty_like(got.plan)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(dev)[0]
+        again, _ = _run_static(case_dev, dev, tile, shift, plan=plan2)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(dev)[0] == free_before
+        assert torch.equal(again.perm, got.perm)
         ref = W.bucket_windows(coords=case["coords"].to(dev), geom=geom, rpb_window=case["window"], tile_rows=tile)
         torch.cuda.synchronize()
         sg, sr = got.stats(), ref.stats()
