@@ -405,6 +405,8 @@ def run_ours(args):
         # the ranks (every block holds two barriers).
         calib = max(max_over_ranks([statistics.median(timed_blocks(rs.run, args.steps, barrier, 3))])[0], 1e-3)
         n_blocks = max(10, min(400, int(600.0 / calib) + 1)) if primary else 5
+        if args.blocks > 0:
+            n_blocks = args.blocks
         n0 = len(sampler.rows) if (sampler and primary) else 0
         blocks = timed_blocks(rs.run, args.steps, barrier, n_blocks)
         n1 = len(sampler.rows) if (sampler and primary) else 0
@@ -766,6 +768,8 @@ def main():
     ap.add_argument("--workload", default="room", choices=["room", "skewed"],
                     help="room: the default line (W-MSA + SW-MSA on a 150k-voxel room); skewed: one 10^6-voxel "
                          "skewed-occupancy scene sharded by window ranges (secondary)")
+    ap.add_argument("--blocks", type=int, default=0,
+                    help="timed blocks of `steps` steps (0: at least 10 and enough for 0.6 s under load)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     args = ap.parse_args()

@@ -12,7 +12,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 constexpr int kMaxStages = 6;
 constexpr int kMaxGroups = 4;
-constexpr int kMaxTile = 64, kMaxProducerWarps = 4;
+constexpr int kMaxTile = 64, kMaxProducerWarps = kMaxStages;
 
 struct AttnParams {
   const void* qkv;
@@ -152,23 +152,39 @@ __device__ __forceinline__ bool stage_table(float* dst, const float* __restrict_
   return true;
 }
 
-// Bias table [rows, H] -> shared memory [rows, stride] (stride >= H, a multiple of four),
-// pre-multiplied by log2 e, pad entries zero.  Called by the first `step` threads of the CTA.
-__device__ __forceinline__ void stage_table_padded(float* dst, const float* __restrict__ src, int rows, int H, int stride,
-                                                   int tid, int step) {
-  const int n = rows * stride;
-  for (int i0 = tid; i0 < n; i0 += step * 8) {
-    float v[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const int i = i0 + k * step;
-      const int r = i / stride, h = i - r * stride;
-      v[k] = (i < n && h < H) ? __ldg(src + r * H + h) : 0.f;
-    }
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (i0 + k * step < n) dst[i0 + k * step] = v[k] * kLog2e;
-  }
+// ---- producer-side plan prefetch ------------------------------------------------------------
+// Work items are dealt to the producer warps whole, and every pipeline stage has exactly one
+// producer warp: warp w owns the stages w, w + PW, ... and gathers the items that fall into them.  (What an item costs its producer is mostly
+// fixed - a few hundred dependent instructions of one warp, about a microsecond - so the warps must
+// not all pay it for every item.  And a stage must have a single producer: a parity wait on the
+// stage's `empty` barrier tells two consecutive phases apart and no more, so the waiter has to see
+// every phase, which a warp that skipped uses of the stage would not.)  Per item a warp needs the
+// item's descriptor and then, at addresses the descriptor gives, the voxel id and metadata word of
+// each row slot.  Both come from the plan in global memory and are requested a few of the warp's own
+// items ahead with asynchronous 4/16-byte copies into small shared-memory rings;
+// cp.async.wait_group keeps exactly the wanted number of requests in flight.
+constexpr int kDescRing = 8, kDescAhead = 4;  // descriptor of the warp's item t + 4 is requested while item t is issued
+constexpr int kVoxRing = 4, kVoxAhead = 2;    // voxel ids / metadata of its item t + 2
+// bytes of plan-prefetch rings one producer warp owns: descriptors, then (voxel id, metadata) pairs
+__host__ __device__ inline int producer_scratch_bytes(int tile) { return kDescRing * 16 + kVoxRing * tile * 8; }
+// Before a timed-out CTA retires: wait (bounded) for the row copies this producer warp submitted
+// and nobody will consume.  The warp owns stages pw, pw + PW, ... (K = S / PW of them) and has
+// submitted `issued` items, the t-th into stage pw + (t % K) * PW as that stage's use t / K; only
+// the latest use of each stage can still be in flight.
+__device__ __forceinline__ void drain_producer(uint64_t* full, int pw, int PW, int S, int issued) {
+  const int K = S / PW;
+  for (int t = issued - 1; t >= 0 && t >= issued - K; --t) mbar_wait_bounded(full + pw + (t % K) * PW, (t / K) & 1);
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // Hardware barrier 1 over the first `n` threads of the CTA (the consumers): the producers do not

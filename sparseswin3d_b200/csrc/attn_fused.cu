@@ -6,12 +6,13 @@
 // with c > tile.
 //
 // Phase A (packs).  CTA b owns every grid-th item of the pack list, walked from its heavy end;
-// item i uses pipeline stage i % S and is computed by consumer group i % G.  The producer warps
-// run ahead: they read the item descriptor and the voxel ids of the item's rows (prefetched a few
-// items ahead in registers) and gather the whole q|k|v rows (3*C contiguous elements each) into
-// the stage with one 1-D bulk (TMA) copy per voxel, completing on the stage's `full` mbarrier;
-// the rows of an item are dealt round-robin to the producer warps, because a warp submits its
-// copies one lane after the other.  The bias table lives in shared memory, staged by the consumers
+// item i uses pipeline stage i % S and is computed by consumer group i % G.  The producer warps run
+// ahead: they read the item descriptor and the voxel ids of the item's rows (requested a few items
+// ahead with small asynchronous copies into shared-memory rings) and gather the whole q|k|v rows
+// (3*C contiguous elements each) into the stage with one 1-D bulk (TMA) copy per voxel, completing
+// on the stage's `full` mbarrier; the rows of an item are dealt round-robin to the producer warps,
+// because a warp submits its copies one lane after the other.  The bias table lives in shared
+// memory, staged by the consumers
 // while the producers already gather.  In a consumer group, thread (hg, r) owns query row r for
 // heads hg, hg+HG, ...: q comes from the staged row, the thread walks the keys of its own window
 // with a chunked online softmax in the log2 domain (dot products and the P.V update are packed
@@ -33,14 +34,15 @@
 
 namespace ssw {
 
-// Shared memory: [barriers 256 B][bias table][stage 0][stage 1]...
-// Stage: [desc int4][vox int[kMaxTile]][rows tile*row_stride]
+// Shared memory: [barriers 256 B][plan-prefetch rings of the producer warps][bias table][stage 0][stage 1]...
+// Stage: [desc int4][item number int, 12 B unused][vox int[kMaxTile]][rows tile*row_stride]
 // Row:   [q | k | v as 3*C floats][meta int2 {byte offset of the key's bias-table row,
 //         region | (query-side relative-position code << 8)}][8 B unused]
 // The 16 bytes after the data skew consecutive rows across the shared-memory banks and carry the
 // per-row metadata, so one base pointer reaches both a key's channels and its metadata.
 constexpr int kBarBytes = 256;
-constexpr int kStageVoxOff = 16;
+constexpr int kStageSeqOff = 16;
+constexpr int kStageVoxOff = 32;
 constexpr int kStageRowsOff = kStageVoxOff + kMaxTile * 4;
 
 // Online-softmax state of one (query row, head).
@@ -335,8 +337,15 @@ __device__ __forceinline__ void store_out(T* dst, const RowState<HD>& st, float 
   }
 }
 
+// MAXT: the most threads a launch of this variant uses.  One CTA per SM; its warps are spread over
+// the SM's four sub-partitions, each with 16384 registers, allocated 8 per thread at a time.
+constexpr int regs_for_threads(int max_threads) {
+  const int warps_per_part = ((max_threads + 31) / 32 + 3) / 4;
+  const int r = (16384 / (warps_per_part * 32)) / 8 * 8;
+  return r > 255 ? 255 : r;
+}
 template <typename T, int HD, bool kTableSmem, int MAXT, bool kSplit>
-__global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
+__global__ void __maxnreg__(regs_for_threads(MAXT)) k_attn_fused(AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   constexpr bool kHalf = sizeof(T) == 2;
   const int tile = p.tile, C = p.C, H = p.H;
@@ -346,9 +355,10 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   uint64_t* gbar = empty + kMaxStages;                   // [kMaxGroups] group-internal barrier
   uint64_t* bbar = gbar + kMaxGroups;                    // phase B copies
   uint64_t* tbar = reinterpret_cast<uint64_t*>(smem) + 30;  // bias table landed
-  float* table_s = reinterpret_cast<float*>(smem + kBarBytes);
+  unsigned char* prod_scratch = smem + kBarBytes;
+  float* table_s = reinterpret_cast<float*>(prod_scratch + p.prod_warps * producer_scratch_bytes(p.tile));
   bool table_ok = true;
-  unsigned char* stage0 = smem + kBarBytes + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
+  unsigned char* stage0 = reinterpret_cast<unsigned char*>(table_s) + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
   const float* table_base = kTableSmem ? table_s : p.table;
   const int gsize = p.group_threads;
   const int gwarps = gsize >> 5;
@@ -392,68 +402,77 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
   const int my_items =
       n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   bool timed_out = !table_ok;
-  int issued = 0;  // producer warps: items whose row copies this warp has submitted
+  int issued = 0;  // producer warps: items this warp has submitted its share of row copies for
   if (is_producer) {
-    // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
-    // of item i+3 (whose descriptor arrived an iteration ago) are requested while item i is issued,
-    // so no iteration waits on a global load.
-    // The rows of an item are dealt round-robin to the producer warps: a warp submits its bulk
-    // copies one lane after the other, so several warps submit several rows at a time.
-    constexpr int kAhead = 3;
+    // The rows of an item are dealt round-robin to the producer warps (a warp submits its bulk
+    // copies one lane after the other, so two warps submit two rows at a time): this warp's j-th
+    // row of an item is row j * PW + pw, lane l looks after j = l and l + 32.  Every producer warp
+    // visits every item, so each of them sees every phase of every `empty` barrier (a parity wait
+    // tells two consecutive phases apart and no more).  Descriptors, voxel ids and metadata come
+    // through the warp's plan-prefetch rings.
     const int PW = p.prod_warps, pw = ((int)threadIdx.x - n_cons) >> 5;
+    const int spw = (tile + PW - 1) / PW;  // rows of an item this warp looks after, at most
+    unsigned char* pscr = prod_scratch + (size_t)pw * producer_scratch_bytes(tile);
+    int4* dring = reinterpret_cast<int4*>(pscr);
+    int2* vring = reinterpret_cast<int2*>(pscr + kDescRing * 16);  // [kVoxRing][spw] {voxel id, metadata}
     // The plan lists packs by ascending occupancy; walking the list backwards puts the long items
     // first and leaves the short ones for the tail of the kernel.
     auto item_index = [&](int k) { return n_small - 1 - ((int)blockIdx.x + k * (int)gridDim.x); };
-    int4 dq[kAhead + 2];
-    int vox[kAhead][2], km[kAhead][2];
-    auto fetch = [&](const int4& d, int (&v)[2], int (&m)[2]) {
-      const int nr = d.z * d.y;
+    for (int t = -kDescAhead; t < my_items; ++t) {
+      const int td = t + kDescAhead;
+      if (lane == 0 && td < my_items) cp_async16(dring + (td & (kDescRing - 1)), p.pack_desc + item_index(td));
+      // every iteration commits one group; what was requested kVoxAhead iterations ago has landed
+      // once at most kVoxAhead - 1 groups are pending: the descriptor of item t + kVoxAhead (asked for
+      // kDescAhead - kVoxAhead iterations before that) and the ids / metadata of item t
+      cp_async_wait<kVoxAhead - 1>();
+      __syncwarp();
+      const int tv = t + kVoxAhead;
+      if (tv >= 0 && tv < my_items) {
+        const int4 d = checked_desc(dring[tv & (kDescRing - 1)], p, true);
+        const int nr = d.z * d.y;
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const int rr = (lane + 32 * k) * PW + pw;
-        v[k] = 0;
-        m[k] = 0;
-        if (rr < nr) {
-          v[k] = __ldg(p.pack_perm + d.x + rr);
-          m[k] = __ldg(p.pack_meta + d.x + rr);
+        for (int k = 0; k < 2; ++k) {
+          const int j = lane + 32 * k, rr = j * PW + pw;
+          if (j < spw && rr < nr) {
+            int2* dst = vring + (tv & (kVoxRing - 1)) * spw + j;
+            cp_async4(&dst->x, p.pack_perm + d.x + rr);
+            cp_async4(&dst->y, p.pack_meta + d.x + rr);
+          }
         }
       }
-    };
+      cp_async_commit();
+      if (t < 0) continue;
+      const int s = t % S, use = t / S;
+      const int4 d_cur = checked_desc(dring[t & (kDescRing - 1)], p, true);
+      const int nr = d_cur.z * d_cur.y;
+      int vox[2], km[2];
 #pragma unroll
-    for (int a = 0; a <= kAhead + 1; ++a)
-      dq[a] = a < my_items ? __ldg(p.pack_desc + item_index(a)) : make_int4(0, 0, 0, 0);
-#pragma unroll
-    for (int a = 0; a < kAhead; ++a) {
-      if (a < my_items) dq[a] = checked_desc(dq[a], p, true);
-      fetch(dq[a], vox[a], km[a]);
-    }
-    for (int i = 0; i < my_items; ++i) {
-      const int s = i % S;
-      const int use = i / S;
-      const int4 d_new = i + kAhead + 2 < my_items
-                             ? __ldg(p.pack_desc + item_index(i + kAhead + 2))
-                             : make_int4(0, 0, 0, 0);
-      int vox_n[2], km_n[2];
-      // the descriptor of item i + kAhead arrived iterations ago: checking it here waits for nothing
-      if (i + kAhead < my_items) dq[kAhead] = checked_desc(dq[kAhead], p, true);
-      fetch(dq[kAhead], vox_n, km_n);  // (an all-zero descriptor fetches nothing)
+      for (int k = 0; k < 2; ++k) {
+        const int j = lane + 32 * k, rr = j * PW + pw;
+        vox[k] = 0;
+        km[k] = 0;
+        if (j < spw && rr < nr) {
+          const int2 e = vring[(t & (kVoxRing - 1)) * spw + j];
+          vox[k] = checked_voxel(e.x, p);
+          km[k] = checked_meta(e.y, p);
+        }
+      }
       if (use > 0 && !mbar_wait_bounded(empty + s, (use - 1) & 1)) {
         timed_out = true;
         break;
       }
       unsigned char* st = stage0 + (size_t)s * p.stage_bytes;
-      const int4 d_cur = dq[0];
-      const int nr = d_cur.z * d_cur.y;
-      if (lane == 0 && pw == 0) *reinterpret_cast<int4*>(st) = d_cur;
+      if (lane == 0 && pw == 0) {
+        *reinterpret_cast<int4*>(st) = d_cur;
+        *reinterpret_cast<int*>(st + kStageSeqOff) = t;
+      }
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int rr = (lane + 32 * k) * PW + pw;
-        if (rr < nr) {
-          vox[0][k] = checked_voxel(vox[0][k], p);  // loaded three items ago: no wait
-          km[0][k] = checked_meta(km[0][k], p);
-          reinterpret_cast<int*>(st + kStageVoxOff)[rr] = vox[0][k];
+        const int j = lane + 32 * k, rr = j * PW + pw;
+        if (j < spw && rr < nr) {
+          reinterpret_cast<int*>(st + kStageVoxOff)[rr] = vox[k];
           *reinterpret_cast<int2*>(st + kStageRowsOff + (size_t)rr * p.row_stride + data_bytes) = make_int2(
-              meta_rel(km[0][k]) * H * 4, meta_region(km[0][k]) | ((meta_rel(km[0][k]) + p.rel_off) << 8));
+              meta_rel(km[k]) * H * 4, meta_region(km[k]) | ((meta_rel(km[k]) + p.rel_off) << 8));
         }
       }
       // rows pw, pw + PW, ... below nr are this warp's
@@ -465,29 +484,14 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       __syncwarp();
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int rr = (lane + 32 * k) * PW + pw;
-        if (rr < nr)
+        const int j = lane + 32 * k, rr = j * PW + pw;
+        if (j < spw && rr < nr)
           bulk_g2s(st + kStageRowsOff + (size_t)rr * p.row_stride + copy_off,
-                   reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[0][k] * 3 * C, copy_bytes, full + s);
+                   reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[k] * 3 * C, copy_bytes, full + s);
       }
-      issued = i + 1;
-#pragma unroll
-      for (int a = 0; a <= kAhead; ++a) dq[a] = dq[a + 1];
-      dq[kAhead + 1] = d_new;
-#pragma unroll
-      for (int a = 0; a + 1 < kAhead; ++a) {
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          vox[a][k] = vox[a + 1][k];
-          km[a][k] = km[a + 1][k];
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        vox[kAhead - 1][k] = vox_n[k];
-        km[kAhead - 1][k] = km_n[k];
-      }
+      issued = t + 1;
     }
+    cp_async_wait<0>();  // nothing of the plan prefetch may still be under way towards this CTA's shared memory
   } else {
     const int g = threadIdx.x / gsize;
     const int ltid = threadIdx.x - g * gsize;
@@ -501,7 +505,14 @@ __global__ void __launch_bounds__(MAXT, 1) k_attn_fused(AttnParams p) {
       const int use = i / S;
       unsigned char* sp = stage0 + (size_t)s * p.stage_bytes;
       unsigned char* rows = sp + kStageRowsOff;
-      if (!mbar_wait_bounded(full + s, use & 1)) {
+      // A group skips the uses of a stage that belong to the other groups, and a parity wait tells
+      // two consecutive phases apart, no more: should the stage still be in the phase before the one
+      // awaited, the wait answers at once.  The item number in the stage header (written before the
+      // producer's arrive) settles it: it can only read i once this use's phase has begun.
+      bool landed = mbar_wait_bounded(full + s, use & 1);
+      for (int again = 0; landed && *reinterpret_cast<volatile const int*>(sp + kStageSeqOff) != i; ++again)
+        landed = again < (1 << 16) && mbar_wait_bounded(full + s, use & 1);
+      if (!landed) {
         timed_out = true;
         break;
       }
@@ -734,18 +745,22 @@ static KernelShape kernel_shape(int tile, int heads, int head_dim, int elt, cons
   (void)elt;
   const int tf = table_entries(rpb_window, heads);
   s.table_floats = tf * 4 <= kTableSmemMax ? tf : 0;
+  // per stage: the stage itself and the plan-prefetch rings of its producer warp
   const size_t fixed = kBarBytes + ((s.table_floats * 4 + 15) & ~15);
-  int stages = (int)((kSmemBudget - fixed) / s.stage_bytes);
+  // (the plan-prefetch rings of the two producer warps are counted once per stage: room to spare)
+  const size_t per_stage = (size_t)s.stage_bytes + producer_scratch_bytes(tile);
+  int stages = (int)((kSmemBudget - fixed) / per_stage);
   if (stages > kMaxStages) stages = kMaxStages;
   s.stages = stages;
-  // one stage is always in flight; at most 1024 threads
+  // One stage is always in flight.  The lane-pair form wants 96 registers per thread, which 20
+  // warps at most can have (five per sub-partition); the other forms run with up to 1024 threads.
+  s.prod_warps = 2;
   int groups = stages - 1;
   if (groups > kMaxGroups) groups = kMaxGroups;
-  s.prod_warps = 2;
-  while (groups > 1 && groups * s.group_threads + 32 * s.prod_warps > (split ? 768 : 1024)) --groups;
+  while (groups > 1 && groups * s.group_threads + 32 * s.prod_warps > (split ? 640 : 1024)) --groups;
   if (groups < 1) groups = 1;
   s.groups = groups;
-  s.smem = fixed + (size_t)(stages > 0 ? stages : 1) * s.stage_bytes;
+  s.smem = fixed + (size_t)(stages > 0 ? stages : 1) * per_stage;
   return s;
 }
 
@@ -756,9 +771,8 @@ static int launch_attn(const AttnParams& p, int threads, size_t smem, cudaStream
   SSW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   if constexpr (sizeof(T) == 4) {
     if (p.split) {
-      if (threads > 768) return SSW_E_UNSUPPORTED;
-      void (*kern)(AttnParams) = threads <= 640 ? k_attn_fused<T, HD, kTableSmem, 640, true>
-                                                : k_attn_fused<T, HD, kTableSmem, 768, true>;
+      if (threads > 640) return SSW_E_UNSUPPORTED;
+      void (*kern)(AttnParams) = k_attn_fused<T, HD, kTableSmem, 640, true>;
       SSW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       SSW_CUDA_TRY(launch_chained(kern, dim3(sms), dim3(threads), smem, stream, p));
       SSW_LAUNCH_CHECK("k_attn_fused");
@@ -855,7 +869,7 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   // fp32 without the COO output: the channels of a (row, head) are split over a lane pair
   bool split = dtype == SSW_F32 && !attn_vals && head_dim % 8 == 0;
   KernelShape s = kernel_shape(tile, heads, head_dim, elt, rpb_window, split);
-  if (split && s.groups * s.group_threads + 32 * s.prod_warps > 768) {
+  if (split && s.groups * s.group_threads + 32 * s.prod_warps > 640) {
     split = false;
     s = kernel_shape(tile, heads, head_dim, elt, rpb_window, false);
   }

@@ -7,28 +7,27 @@
 //
 //   * The plan is *padded*: inside a pack every window gets a run of row slots rounded up to
 //     1, 2, 4, 8, 16, 32, 48 or 64, so a 16-slot MMA tile holds whole windows (several when c < 16)
-//     or a 16-row slice of one window.  Unused slots keep whatever an earlier item left in their
-//     q and k parts (their scores are replaced, not multiplied, so the contents do not matter) and
-//     get their v part zeroed by the producer (p = 0 times a stale Inf would be NaN); their query
-//     rows are never stored.
+//     or a 16-row slice of one window.  Unused slots keep whatever an earlier item left in them;
+//     as keys they are never read: the ldmatrix row addresses of unused slots point at a row of
+//     zeros instead (their scores then get -inf and their probabilities are 0; -inf plus a NaN
+//     score or 0 times a stale Inf would be NaN).  As queries they give rows that are never stored.
 //   * Q comes in as A fragments (ldmatrix), K as B fragments (ldmatrix), S = Q K^T lands in fp32
 //     accumulators whose layout is also the A layout of the next MMA, so P = softmax(S) is packed
 //     to 16 bit in registers and multiplied with V (ldmatrix.trans).
-//   * Windows of up to 16 voxels (nine in ten on a surface scene): a warp takes a 16-slot tile and
-//     walks all heads inside it, so the per-key metadata, the window / region comparisons and the
-//     bias rows (one 16-byte load per (query, key) pair brings four heads) are worked out once per
-//     tile.  Larger windows: a unit of work is (16-slot tile, head) looping over 16-key blocks with
-//     an online softmax.
+//   * A unit of work is (16-slot tile, head).  Windows of up to 16 voxels (nine in ten on a surface
+//     scene) see one block of 16 keys: scores, row maximum (from 0), probabilities and the output
+//     in one straight pass.  Larger windows loop over 16-key blocks with an online softmax.
+//   * All consumer warps work on the same item, each on its own units, so an item's stage is held
+//     for about one unit's time and the other stages of the ring are copies in flight: what bounds
+//     this kernel is how far the row gathers run ahead, not the arithmetic.
 //   * Softmax keeps upstream's semantics: the running maximum starts at 0, the denominator gets
-//     +1e-8; bias from the shared-memory table (pre-multiplied by log2 e, heads padded to a
-//     multiple of four), -100 shift mask.
+//     +1e-8; bias from the shared-memory table (pre-multiplied by log2 e), -100 shift mask.
 //   * Outputs go from the accumulator registers straight to the voxels' rows.
 //   * Values that are not finite: upstream confines them to their own window; here a v row that
 //     holds Inf or NaN also spoils the other windows that share its 16-slot tile (p = 0 for those
 //     keys, and 0 * Inf is NaN inside the MMA).
 //
-// Phase 1 (packs): every consumer group of four warps takes whole work items, one per pipeline
-// stage.  Phase 2 (windows with more voxels than a pack holds): a work item is one tile of query
+// Phase 1 (packs): one work item per pipeline stage.  Phase 2 (windows with more voxels than a pack holds): a work item is one tile of query
 // rows of such a window; its q rows sit in stage 0 while the window's k|v rows stream through the
 // other stages tile by tile, and all consumer warps work on the same key tile, each on its own
 // (16 query rows, head) unit whose accumulators stay in registers for the whole window.
@@ -39,6 +38,8 @@
 namespace ssw {
 
 constexpr int kMmaGroupWarps = 4;
+constexpr int kMmaGroups = 3;  // 12 consumer warps: with up to six producer warps 576 threads, 96 registers each
+
 constexpr int kMmaStageVoxOff = 16;
 constexpr int kMmaStageRowsOff = kMmaStageVoxOff + kMaxTile * 4;
 // Layout of a staged row's metadata word .y: region (5 bits), window inside the pack (7 bits: 0..63,
@@ -76,14 +77,16 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ int2 row_meta(int m, int window, int rel_off) {
   return make_int2(meta_rel(m), meta_region(m) | (window << 5) | ((meta_rel(m) + rel_off) << kMmaRelShift));
 }
-// zero the v part (C elements from byte 2*C*sizeof(T)) of a staged row
-template <typename T>
-__device__ __forceinline__ void zero_v(unsigned char* row, int C) {
-  uint4* v = reinterpret_cast<uint4*>(row + 2 * C * sizeof(T));
-  for (int i = 0; i < (C * (int)sizeof(T)) / 16; ++i) v[i] = make_uint4(0, 0, 0, 0);
-}
 __device__ __forceinline__ int2 pad_meta(int rel_off) {
   return make_int2(0, (kMmaPadWindow << 5) | (rel_off << kMmaRelShift));
+}
+__device__ __forceinline__ bool is_pad_meta(int me_y) { return ((me_y >> 5) & 127) == kMmaPadWindow; }
+// Where ldmatrix reads slot `slot` as a key (k and v slices): the staged row, or a row of zeros for
+// an unused slot.
+__device__ __forceinline__ const unsigned char* key_row(const unsigned char* rows, int row_stride, int data_bytes, int slot,
+                                                        const unsigned char* zero_row) {
+  const unsigned char* r = rows + (size_t)slot * row_stride;
+  return is_pad_meta(reinterpret_cast<const int2*>(r + data_bytes)->y) ? zero_row : r;
 }
 
 // Bias of (query row meta .y, key meta .x) for head h, in the log2 domain.  `tstride`: floats per
@@ -101,115 +104,104 @@ __device__ __forceinline__ float pair_mask(int x) {
   return (kMask && (x & 31)) ? -100.0f * kLog2e : 0.f;
 }
 
-// A 16-slot tile whose windows hold at most 16 voxels: the tile's 16 slots are also its keys.  The
-// warp walks all heads; everything that does not depend on the head is computed once.
+// One (16-slot tile, head) unit whose windows hold at most 16 voxels: the tile's 16 slots are also
+// its keys, so there is one block of scores and no running state.
 template <typename T, int HD, bool kTableSmem, bool kMask>
-__device__ __forceinline__ void tile_all_heads(const unsigned char* rows, int row_stride, int data_bytes, const int* svox,
-                                               int slot0, int H, int C, const float* table_base, int tstride,
-                                               float qscale, T* out, int lane) {
+__device__ __forceinline__ void tile_head(const unsigned char* rows, int row_stride, int data_bytes, const int* svox,
+                                          const unsigned char* zero_row, int slot0, int h, int C, const float* table_base,
+                                          int tstride, float qscale, T* out, int lane) {
   const int qr = lane >> 2, qt = lane & 3, mi = lane >> 3;
   const unsigned char* r_lo = rows + (size_t)(slot0 + qr) * row_stride;
   const unsigned char* r_hi = r_lo + 8 * (size_t)row_stride;
   const int me_lo = reinterpret_cast<const int2*>(r_lo + data_bytes)->y;
   const int me_hi = reinterpret_cast<const int2*>(r_hi + data_bytes)->y;
-  const int v_lo = svox[slot0 + qr], v_hi = svox[slot0 + qr + 8];
+  const int hoff = h * HD * (int)sizeof(T);
+  const unsigned char* qp =
+      rows + (size_t)(slot0 + (mi & 1) * 8 + (lane & 7)) * row_stride + hoff + (mi >> 1) * 8 * sizeof(T);
+  const unsigned char* kp = key_row(rows, row_stride, data_bytes, slot0 + (mi >> 1) * 8 + (lane & 7), zero_row) + hoff +
+                            (C + (mi & 1) * 8) * sizeof(T);
+  const unsigned char* vp = key_row(rows, row_stride, data_bytes, slot0 + (mi & 1) * 8 + (lane & 7), zero_row) + hoff +
+                            (2 * C + (mi >> 1) * 8) * sizeof(T);
+  float sacc[2][4];
+#pragma unroll
+  for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+    uint32_t qf[4], kf[4];
+    ldmatrix_x4(qf, qp + ks * 16 * sizeof(T));
+    ldmatrix_x4(kf, kp + ks * 16 * sizeof(T));
+    mma16816<T>(sacc[0], qf, kf[0], kf[1]);
+    mma16816<T>(sacc[1], qf, kf[2], kf[3]);
+  }
+  // the V fragments do not depend on the scores: request them before the softmax arithmetic
+  uint32_t vf[HD / 16][4];
+#pragma unroll
+  for (int n = 0; n < HD / 16; ++n) ldmatrix_x4_trans(vf[n], vp + n * 16 * sizeof(T));
   // column j of this lane: key slot n*8 + qt*2 + e with j = n*2 + e
-  float madd_lo[4], madd_hi[4];
-  int kx[4];
+  float s_lo[4], s_hi[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int ks = slot0 + (j >> 1) * 8 + qt * 2 + (j & 1);
     const int2 km = *reinterpret_cast<const int2*>(rows + (size_t)ks * row_stride + data_bytes);
-    kx[j] = km.x;
-    madd_lo[j] = pair_mask<kMask>(km.y ^ me_lo);
-    madd_hi[j] = pair_mask<kMask>(km.y ^ me_hi);
+    s_lo[j] = fmaf(sacc[j >> 1][j & 1], qscale, bias_of<kTableSmem>(table_base, tstride, me_lo, km.x, h)) +
+              pair_mask<kMask>(km.y ^ me_lo);
+    s_hi[j] = fmaf(sacc[j >> 1][2 + (j & 1)], qscale, bias_of<kTableSmem>(table_base, tstride, me_hi, km.x, h)) +
+              pair_mask<kMask>(km.y ^ me_hi);
   }
-  const unsigned char* qp = rows + (size_t)(slot0 + (mi & 1) * 8 + (lane & 7)) * row_stride + (mi >> 1) * 8 * sizeof(T);
-  const unsigned char* kp = rows + (size_t)(slot0 + (mi >> 1) * 8 + (lane & 7)) * row_stride + (C + (mi & 1) * 8) * sizeof(T);
-  const unsigned char* vp = rows + (size_t)(slot0 + (mi & 1) * 8 + (lane & 7)) * row_stride + (2 * C + (mi >> 1) * 8) * sizeof(T);
-  T* o_lo = out + (int64_t)(v_lo < 0 ? 0 : v_lo) * C + qt * 2;
-  T* o_hi = out + (int64_t)(v_hi < 0 ? 0 : v_hi) * C + qt * 2;
-  for (int h0 = 0; h0 < H; h0 += 4) {
-    // biases of the lane's eight (row, column) pairs for four heads at a time
-    float4 b_lo[4], b_hi[4];
-    if constexpr (kTableSmem) {
+  // the row maximum starts from 0 (ops.cu:137)
+  float m_lo = fmaxf(fmaxf(s_lo[0], s_lo[1]), fmaxf(s_lo[2], s_lo[3]));
+  float m_hi = fmaxf(fmaxf(s_hi[0], s_hi[1]), fmaxf(s_hi[2], s_hi[3]));
+  m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
+  m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
+  m_lo = fmaxf(fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2)), 0.f);
+  m_hi = fmaxf(fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2)), 0.f);
+  float p_lo[4], p_hi[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        b_lo[j] = *reinterpret_cast<const float4*>(table_base + ((me_lo >> kMmaRelShift) - kx[j]) * tstride + h0);
-        b_hi[j] = *reinterpret_cast<const float4*>(table_base + ((me_hi >> kMmaRelShift) - kx[j]) * tstride + h0);
-      }
+  for (int j = 0; j < 4; ++j) {
+    p_lo[j] = fast_exp2(s_lo[j] - m_lo);
+    p_hi[j] = fast_exp2(s_hi[j] - m_hi);
+  }
+  float l_lo = (p_lo[0] + p_lo[1]) + (p_lo[2] + p_lo[3]);
+  float l_hi = (p_hi[0] + p_hi[1]) + (p_hi[2] + p_hi[3]);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  uint32_t pf[4];
+  pf[0] = pack2<T>(p_lo[0], p_lo[1]);
+  pf[1] = pack2<T>(p_hi[0], p_hi[1]);
+  pf[2] = pack2<T>(p_lo[2], p_lo[3]);
+  pf[3] = pack2<T>(p_hi[2], p_hi[3]);
+  // bf16 keeps 8 bits of a probability: the rounding residual goes through a second MMA (see
+  // unit_key_block)
+  constexpr bool kSplitP = std::is_same<T, __nv_bfloat16>::value;
+  uint32_t pl[4];
+  if constexpr (kSplitP) {
+    pl[0] = pack2<T>(p_lo[0] - __uint_as_float(pf[0] << 16), p_lo[1] - __uint_as_float(pf[0] & 0xffff0000u));
+    pl[1] = pack2<T>(p_hi[0] - __uint_as_float(pf[1] << 16), p_hi[1] - __uint_as_float(pf[1] & 0xffff0000u));
+    pl[2] = pack2<T>(p_lo[2] - __uint_as_float(pf[2] << 16), p_lo[3] - __uint_as_float(pf[2] & 0xffff0000u));
+    pl[3] = pack2<T>(p_hi[2] - __uint_as_float(pf[3] << 16), p_hi[3] - __uint_as_float(pf[3] & 0xffff0000u));
+  }
+  const float inv_lo = __frcp_rn(l_lo + 1e-8f), inv_hi = __frcp_rn(l_hi + 1e-8f);  // ops.cu:164
+  const int v_lo = svox[slot0 + qr], v_hi = svox[slot0 + qr + 8];
+  T* o_lo = out + (int64_t)(v_lo < 0 ? 0 : v_lo) * C + h * HD + qt * 2;
+  T* o_hi = out + (int64_t)(v_hi < 0 ? 0 : v_hi) * C + h * HD + qt * 2;
+#pragma unroll
+  for (int n = 0; n < HD / 16; ++n) {
+    float oa[4] = {0.f, 0.f, 0.f, 0.f}, ob[4] = {0.f, 0.f, 0.f, 0.f};
+    mma16816<T>(oa, pf, vf[n][0], vf[n][1]);
+    mma16816<T>(ob, pf, vf[n][2], vf[n][3]);
+    if constexpr (kSplitP) {
+      mma16816<T>(oa, pl, vf[n][0], vf[n][1]);
+      mma16816<T>(ob, pl, vf[n][2], vf[n][3]);
     }
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const int h = h0 + t;
-      if (h >= H) break;
-      const int hoff = h * HD * (int)sizeof(T);
-      float sacc[2][4];
-#pragma unroll
-      for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        uint32_t qf[4], kf[4];
-        ldmatrix_x4(qf, qp + hoff + ks * 16 * sizeof(T));
-        ldmatrix_x4(kf, kp + hoff + ks * 16 * sizeof(T));
-        mma16816<T>(sacc[0], qf, kf[0], kf[1]);
-        mma16816<T>(sacc[1], qf, kf[2], kf[3]);
-      }
-      float s_lo[4], s_hi[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float bl, bh;
-        if constexpr (kTableSmem) {
-          bl = t == 0 ? b_lo[j].x : t == 1 ? b_lo[j].y : t == 2 ? b_lo[j].z : b_lo[j].w;
-          bh = t == 0 ? b_hi[j].x : t == 1 ? b_hi[j].y : t == 2 ? b_hi[j].z : b_hi[j].w;
-        } else {
-          bl = bias_of<false>(table_base, tstride, me_lo, kx[j], h);
-          bh = bias_of<false>(table_base, tstride, me_hi, kx[j], h);
-        }
-        s_lo[j] = fmaf(sacc[j >> 1][j & 1], qscale, bl) + madd_lo[j];
-        s_hi[j] = fmaf(sacc[j >> 1][2 + (j & 1)], qscale, bh) + madd_hi[j];
-      }
-      // the row maximum starts from 0 (ops.cu:137)
-      float m_lo = fmaxf(fmaxf(s_lo[0], s_lo[1]), fmaxf(s_lo[2], s_lo[3]));
-      float m_hi = fmaxf(fmaxf(s_hi[0], s_hi[1]), fmaxf(s_hi[2], s_hi[3]));
-      m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
-      m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
-      m_lo = fmaxf(fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2)), 0.f);
-      m_hi = fmaxf(fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2)), 0.f);
-      float p_lo[4], p_hi[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        p_lo[j] = fast_exp2(s_lo[j] - m_lo);
-        p_hi[j] = fast_exp2(s_hi[j] - m_hi);
-      }
-      float l_lo = (p_lo[0] + p_lo[1]) + (p_lo[2] + p_lo[3]);
-      float l_hi = (p_hi[0] + p_hi[1]) + (p_hi[2] + p_hi[3]);
-      l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-      l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-      l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-      l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-      uint32_t pf[4];
-      pf[0] = pack2<T>(p_lo[0], p_lo[1]);
-      pf[1] = pack2<T>(p_hi[0], p_hi[1]);
-      pf[2] = pack2<T>(p_lo[2], p_lo[3]);
-      pf[3] = pack2<T>(p_hi[2], p_hi[3]);
-      const float inv_lo = 1.0f / (l_lo + 1e-8f), inv_hi = 1.0f / (l_hi + 1e-8f);  // ops.cu:164
-#pragma unroll
-      for (int n = 0; n < HD / 8; n += 2) {
-        uint32_t vf[4];
-        float oa[4] = {0.f, 0.f, 0.f, 0.f}, ob[4] = {0.f, 0.f, 0.f, 0.f};
-        ldmatrix_x4_trans(vf, vp + hoff + n * 8 * sizeof(T));
-        mma16816<T>(oa, pf, vf[0], vf[1]);
-        mma16816<T>(ob, pf, vf[2], vf[3]);
-        if (v_lo >= 0) {
-          *reinterpret_cast<uint32_t*>(o_lo + h * HD + n * 8) = pack2<T>(oa[0] * inv_lo, oa[1] * inv_lo);
-          *reinterpret_cast<uint32_t*>(o_lo + h * HD + n * 8 + 8) = pack2<T>(ob[0] * inv_lo, ob[1] * inv_lo);
-        }
-        if (v_hi >= 0) {
-          *reinterpret_cast<uint32_t*>(o_hi + h * HD + n * 8) = pack2<T>(oa[2] * inv_hi, oa[3] * inv_hi);
-          *reinterpret_cast<uint32_t*>(o_hi + h * HD + n * 8 + 8) = pack2<T>(ob[2] * inv_hi, ob[3] * inv_hi);
-        }
-      }
+    if (v_lo >= 0) {
+      *reinterpret_cast<uint32_t*>(o_lo + n * 16) = pack2<T>(oa[0] * inv_lo, oa[1] * inv_lo);
+      *reinterpret_cast<uint32_t*>(o_lo + n * 16 + 8) = pack2<T>(ob[0] * inv_lo, ob[1] * inv_lo);
+    }
+    if (v_hi >= 0) {
+      *reinterpret_cast<uint32_t*>(o_hi + n * 16) = pack2<T>(oa[2] * inv_hi, oa[3] * inv_hi);
+      *reinterpret_cast<uint32_t*>(o_hi + n * 16 + 8) = pack2<T>(ob[2] * inv_hi, ob[3] * inv_hi);
     }
   }
 }
@@ -246,13 +238,14 @@ __device__ __forceinline__ void unit_begin(MmaUnit<HD>& u, const unsigned char* 
 // k_off / v_off: byte offsets of this head's k and v slices inside a staged row.
 template <typename T, int HD, bool kTableSmem, bool kMask>
 __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned char* rows, int row_stride, int data_bytes,
-                                               int ks0, int k_off, int v_off, const float* table_base, int tstride, int h,
-                                               float qscale, int lane) {
+                                               const unsigned char* zero_row, int ks0, int k_off, int v_off,
+                                               const float* table_base, int tstride, int h, float qscale, int lane) {
   const int qt = lane & 3, mi = lane >> 3;
   float sacc[2][4];
 #pragma unroll
   for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
-  const unsigned char* kp = rows + (size_t)(ks0 + (mi >> 1) * 8 + (lane & 7)) * row_stride + k_off + (mi & 1) * 8 * sizeof(T);
+  const unsigned char* kp =
+      key_row(rows, row_stride, data_bytes, ks0 + (mi >> 1) * 8 + (lane & 7), zero_row) + k_off + (mi & 1) * 8 * sizeof(T);
 #pragma unroll
   for (int ks = 0; ks < HD / 16; ++ks) {
     uint32_t kf[4];
@@ -308,13 +301,30 @@ __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned ch
   pf[1] = pack2<T>(p02, p03);
   pf[2] = pack2<T>(p10, p11);
   pf[3] = pack2<T>(p12, p13);
-  const unsigned char* vp = rows + (size_t)(ks0 + (mi & 1) * 8 + (lane & 7)) * row_stride + v_off + (mi >> 1) * 8 * sizeof(T);
+  // bf16 keeps 8 bits of a probability.  The absolute error that leaves in an output is bounded by
+  // 2^-8 * sum p|v|, which a row that averages hundreds of keys (small output, by cancellation) does
+  // not forgive.  The rounding residual goes through a second MMA (the tensor pipe is far from
+  // busy), which leaves the output rounding as the only 16-bit step after the scores.
+  constexpr bool kSplitP = std::is_same<T, __nv_bfloat16>::value;
+  uint32_t pl[4];
+  if constexpr (kSplitP) {
+    pl[0] = pack2<T>(p00 - __uint_as_float(pf[0] << 16), p01 - __uint_as_float(pf[0] & 0xffff0000u));
+    pl[1] = pack2<T>(p02 - __uint_as_float(pf[1] << 16), p03 - __uint_as_float(pf[1] & 0xffff0000u));
+    pl[2] = pack2<T>(p10 - __uint_as_float(pf[2] << 16), p11 - __uint_as_float(pf[2] & 0xffff0000u));
+    pl[3] = pack2<T>(p12 - __uint_as_float(pf[3] << 16), p13 - __uint_as_float(pf[3] & 0xffff0000u));
+  }
+  const unsigned char* vp =
+      key_row(rows, row_stride, data_bytes, ks0 + (mi & 1) * 8 + (lane & 7), zero_row) + v_off + (mi >> 1) * 8 * sizeof(T);
 #pragma unroll
   for (int n = 0; n < HD / 8; n += 2) {
     uint32_t vf[4];
     ldmatrix_x4_trans(vf, vp + n * 8 * sizeof(T));
     mma16816<T>(u.o[n], pf, vf[0], vf[1]);
     mma16816<T>(u.o[n + 1], pf, vf[2], vf[3]);
+    if constexpr (kSplitP) {
+      mma16816<T>(u.o[n], pl, vf[0], vf[1]);
+      mma16816<T>(u.o[n + 1], pl, vf[2], vf[3]);
+    }
   }
 }
 
@@ -331,7 +341,7 @@ __device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, const int* svo
   ll += __shfl_xor_sync(0xffffffffu, ll, 2);
   lh += __shfl_xor_sync(0xffffffffu, lh, 1);
   lh += __shfl_xor_sync(0xffffffffu, lh, 2);
-  const float inv_lo = 1.0f / (ll + 1e-8f), inv_hi = 1.0f / (lh + 1e-8f);  // ops.cu:164
+  const float inv_lo = __frcp_rn(ll + 1e-8f), inv_hi = __frcp_rn(lh + 1e-8f);  // ops.cu:164
   const int v_lo = svox[slot0 + qr], v_hi = svox[slot0 + qr + 8];
   if (v_lo >= 0) {
     T* o = out + (int64_t)v_lo * C + h * HD + qt * 2;
@@ -346,7 +356,8 @@ __device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, const int* svo
 }
 
 template <typename T, int HD, bool kTableSmem, bool kMask>
-__global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxProducerWarps, 1) k_attn_mma(AttnParams p) {
+__global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMmaGroups + 32 * kMaxProducerWarps, 1) k_attn_mma(AttnParams p) {
+  // p.prod_warps == p.stages: one producer warp per pipeline stage
   extern __shared__ __align__(16) unsigned char smem[];
   const int tile = p.tile, C = p.C, H = p.H;
   const int S = p.stages, G = p.groups;
@@ -357,10 +368,14 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   uint64_t* qfull = dempty + kMaxStages;                // phase 2: query tile landed
   uint64_t* qempty = qfull + 1;                         // phase 2: query stage may be refilled
   uint64_t* tbar = reinterpret_cast<uint64_t*>(smem) + 30;  // bias table landed
-  float* table_s = reinterpret_cast<float*>(smem + 256);
-  unsigned char* stage0 = smem + 256 + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
+  // [barriers 256 B][plan-prefetch rings of the producer warps][row of zeros, row_stride B][bias table][stages]
+  unsigned char* prod_scratch = smem + 256;
+  unsigned char* zero_row = prod_scratch + p.prod_warps * producer_scratch_bytes(p.tile);
+  float* table_s = reinterpret_cast<float*>(zero_row + p.row_stride);
+  bool table_ok = true;
+  unsigned char* stage0 = reinterpret_cast<unsigned char*>(table_s) + (kTableSmem ? ((p.table_floats * 4 + 15) & ~15) : 0);
   const float* table_base = kTableSmem ? table_s : p.table;
-  const int tstride = kTableSmem ? ((H + 3) & ~3) : H;  // floats per bias-table row
+  const int tstride = H;  // floats per bias-table row
   const int gsize = kMmaGroupWarps * 32;
   const int n_cons = gsize * G;
   const int n_cons_warps = G * kMmaGroupWarps;
@@ -372,22 +387,24 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
-      mbar_init(full + s, PW);               // one arrive (with its byte count) per producer warp
-      mbar_init(empty + s, kMmaGroupWarps);  // every warp of the consuming group hands the stage back
+      mbar_init(full + s, 1);                // one producer warp gathers an item: its arrive carries the byte count
+      mbar_init(empty + s, n_cons_warps);    // every consumer warp hands the stage back
       mbar_init(dfull + s, PW);
       mbar_init(dempty + s, n_cons_warps);   // every consumer warp works on every key tile
     }
     mbar_init(qfull, PW);
     mbar_init(qempty, n_cons_warps);
+    mbar_init(tbar, 1);
     mbar_fence_init();
   }
+  for (int i = threadIdx.x; i < p.row_stride / 16; i += blockDim.x) reinterpret_cast<uint4*>(zero_row)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
   grid_dependency_wait();
   const int n_items = checked_count(p.header[SSW_H_PACKS], p);
   const int n_small = min(checked_count(p.header[SSW_H_PACKS_SMALL], p), n_items);
   if constexpr (kTableSmem) {
     if (!is_producer) {  // the producers are already gathering the first items
-      stage_table_padded(table_s, p.table, p.table_floats / tstride, H, tstride, threadIdx.x, n_cons);
+      table_ok = stage_table(table_s, p.table, p.table_floats, threadIdx.x, n_cons, tbar);
       consumer_sync(n_cons);
     }
   }
@@ -396,115 +413,102 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
   // Phase 1: packs
   // ------------------------------------------------------------------------------------------
   const int my_items = n_small > (int)blockIdx.x ? (n_small - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  bool timed_out = false;
-  int issued = 0;  // producer warps: phase-1 items whose row copies this warp has submitted
+  bool timed_out = !table_ok;
+  int issued = 0;  // producer warps: how many of its phase-1 items this warp has submitted row copies for
   if (is_producer) {
     // slot -> row of the pack: window wl = slot / cpad, i = slot % cpad, valid if wl < nwin && i < c.
-    // Register pipeline, three items deep: the descriptor of item i+5 and the voxel ids / metadata
-    // of item i+3 (whose descriptor arrived an iteration ago) are requested while item i is issued,
-    // so no iteration waits on a global load.
-    // The rows of an item are dealt round-robin to the producer warps: a warp submits its bulk
-    // copies one lane after the other, so several warps submit several rows at a time.
-    constexpr int kAhead = 3;
+    // This warp gathers the items pw, pw + S, ... of the CTA into stage pw (PW == S), lane l looking
+    // after slots l and l + 32; descriptors, voxel ids and metadata come through the warp's
+    // plan-prefetch rings.
+    unsigned char* pscr = prod_scratch + (size_t)pw * producer_scratch_bytes(tile);
+    int4* dring = reinterpret_cast<int4*>(pscr);
+    int2* vring = reinterpret_cast<int2*>(pscr + kDescRing * 16);  // [kVoxRing][tile] {voxel id, metadata}
     // The plan lists packs by ascending occupancy; walking the list backwards puts the long items
     // first and leaves the short ones for the tail of the kernel.
     auto item_index = [&](int k) { return n_small - 1 - ((int)blockIdx.x + k * (int)gridDim.x); };
-    int4 dq[kAhead + 2];
-    int vox[kAhead][2], km[kAhead][2];
-    auto fetch = [&](const int4& d, int (&v)[2], int (&m)[2]) {
-      const int c = d.y, cpad = slots_of_window(c > 0 ? c : 1, 1);
+    const int n_mine = my_items > pw ? (my_items - pw + PW - 1) / PW : 0;
+    for (int t = -kDescAhead; t < n_mine; ++t) {
+      const int td = t + kDescAhead;
+      if (lane == 0 && td < n_mine) cp_async16(dring + (td & (kDescRing - 1)), p.pack_desc + item_index(pw + td * PW));
+      // every iteration commits one group; what was requested kVoxAhead iterations ago has landed
+      // once at most kVoxAhead - 1 groups are pending: the descriptor of item t + kVoxAhead (asked for
+      // kDescAhead - kVoxAhead iterations before that) and the ids / metadata of item t
+      cp_async_wait<kVoxAhead - 1>();
+      __syncwarp();
+      const int tv = t + kVoxAhead;
+      if (tv >= 0 && tv < n_mine) {
+        const int4 d = checked_desc(dring[tv & (kDescRing - 1)], p, true);
+        const int c = d.y, cpad = slots_of_window(c, 1);
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const int slot = (lane + 32 * k) * PW + pw;
-        const int wl = slot / cpad, i = slot - wl * cpad;
-        v[k] = -1;
-        m[k] = 0;
-        if (slot < tile && wl < d.z && i < c) {
-          v[k] = __ldg(p.pack_perm + d.x + wl * c + i);
-          // the in-window position is not needed here: its bits carry the window's index in the pack
-          m[k] = (__ldg(p.pack_meta + d.x + wl * c + i) & ~1023) | wl;
+        for (int k = 0; k < 2; ++k) {
+          const int slot = lane + 32 * k;
+          const int wl = slot / cpad, ii = slot - wl * cpad;
+          if (slot < tile && wl < d.z && ii < c) {
+            int2* dst = vring + (tv & (kVoxRing - 1)) * tile + slot;
+            cp_async4(&dst->x, p.pack_perm + d.x + wl * c + ii);
+            cp_async4(&dst->y, p.pack_meta + d.x + wl * c + ii);
+          }
         }
       }
-    };
+      cp_async_commit();
+      if (t < 0) continue;
+      const int s = pw, use = t;  // item pw + t * S
+      const int4 d_cur = checked_desc(dring[t & (kDescRing - 1)], p, true);
+      int vox[2], km[2];
+      {
+        const int c = d_cur.y, cpad = slots_of_window(c, 1);
 #pragma unroll
-    for (int a = 0; a <= kAhead + 1; ++a)
-      dq[a] = a < my_items ? __ldg(p.pack_desc + item_index(a)) : make_int4(0, 0, 0, 0);
-#pragma unroll
-    for (int a = 0; a < kAhead; ++a) {
-      if (a < my_items) dq[a] = checked_desc(dq[a], p, true);
-      fetch(dq[a], vox[a], km[a]);
-    }
-    for (int i = 0; i < my_items; ++i) {
-      const int s = i % S;
-      const int use = i / S;
-      const int4 d_new = i + kAhead + 2 < my_items
-                             ? __ldg(p.pack_desc + item_index(i + kAhead + 2))
-                             : make_int4(0, 0, 0, 0);
-      int vox_n[2], km_n[2];
-      // the descriptor of item i + kAhead arrived iterations ago: checking it here waits for nothing
-      if (i + kAhead < my_items) dq[kAhead] = checked_desc(dq[kAhead], p, true);
-      fetch(dq[kAhead], vox_n, km_n);  // (an all-zero descriptor fetches nothing)
+        for (int k = 0; k < 2; ++k) {
+          const int slot = lane + 32 * k;
+          const int wl = slot / cpad, ii = slot - wl * cpad;
+          vox[k] = -1;
+          km[k] = 0;
+          if (slot < tile && wl < d_cur.z && ii < c) {
+            const int2 e = vring[(t & (kVoxRing - 1)) * tile + slot];
+            vox[k] = checked_voxel(e.x, p);
+            // the in-window position is not needed here: its bits carry the window's index in the pack
+            km[k] = (checked_meta(e.y, p) & ~1023) | wl;
+          }
+        }
+      }
       if (use > 0 && !mbar_wait_bounded(empty + s, (use - 1) & 1)) {
         timed_out = true;
         break;
       }
       unsigned char* st = stage0 + (size_t)s * p.stage_bytes;
-      const int4 d_cur = dq[0];
-      if (lane == 0 && pw == 0) *reinterpret_cast<int4*>(st) = d_cur;
+      if (lane == 0) *reinterpret_cast<int4*>(st) = d_cur;
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int slot = (lane + 32 * k) * PW + pw;
+        const int slot = lane + 32 * k;
         if (slot < tile) {
-          if (vox[0][k] >= 0) {  // loaded three items ago: no wait
-            vox[0][k] = checked_voxel(vox[0][k], p);
-            km[0][k] = checked_meta(km[0][k], p);
-          }
-          reinterpret_cast<int*>(st + kMmaStageVoxOff)[slot] = vox[0][k];
+          reinterpret_cast<int*>(st + kMmaStageVoxOff)[slot] = vox[k];
           // Unused slots form a window of their own with neutral codes, so their (discarded) scores
-          // index inside the bias table; their v part must not hold a stale Inf or NaN.
-          unsigned char* row = st + kMmaStageRowsOff + (size_t)slot * p.row_stride;
-          *reinterpret_cast<int2*>(row + data_bytes) =
-              vox[0][k] >= 0 ? row_meta(km[0][k], km[0][k] & 1023, p.rel_off) : pad_meta(p.rel_off);
-          if (vox[0][k] < 0) zero_v<T>(row, C);
+          // index inside the bias table.
+          *reinterpret_cast<int2*>(st + kMmaStageRowsOff + (size_t)slot * p.row_stride + data_bytes) =
+              vox[k] >= 0 ? row_meta(km[k], km[k] & 1023, p.rel_off) : pad_meta(p.rel_off);
         }
       }
-      const int my_rows = __popc(__ballot_sync(0xffffffffu, vox[0][0] >= 0)) + __popc(__ballot_sync(0xffffffffu, vox[0][1] >= 0));
-      // Zeroed v parts were written through the generic proxy; a later item's bulk copy may land on
-      // them.  The arrive releases the stage to the consumers: every lane's stores come before it,
-      // and the warp's copies after the byte count they complete against is announced.
-      fence_async_smem();
+      const int my_rows = __popc(__ballot_sync(0xffffffffu, vox[0] >= 0)) + __popc(__ballot_sync(0xffffffffu, vox[1] >= 0));
+      // The arrive releases the stage to the consumers: every lane's metadata stores come before
+      // it, and the warp's copies after the byte count they complete against is announced.
       __syncwarp();
       if (lane == 0) mbar_expect_tx(full + s, (uint32_t)my_rows * (uint32_t)data_bytes);
       __syncwarp();
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        const int slot = (lane + 32 * k) * PW + pw;
-        if (slot < tile && vox[0][k] >= 0)
+        const int slot = lane + 32 * k;
+        if (slot < tile && vox[k] >= 0)
           bulk_g2s(st + kMmaStageRowsOff + (size_t)slot * p.row_stride,
-                   reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[0][k] * 3 * C, data_bytes, full + s);
+                   reinterpret_cast<const T*>(p.qkv) + (int64_t)vox[k] * 3 * C, data_bytes, full + s);
       }
-      issued = i + 1;
-#pragma unroll
-      for (int a = 0; a <= kAhead; ++a) dq[a] = dq[a + 1];
-      dq[kAhead + 1] = d_new;
-#pragma unroll
-      for (int a = 0; a + 1 < kAhead; ++a) {
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          vox[a][k] = vox[a + 1][k];
-          km[a][k] = km[a + 1][k];
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        vox[kAhead - 1][k] = vox_n[k];
-        km[kAhead - 1][k] = km_n[k];
-      }
+      issued = t + 1;
     }
+    cp_async_wait<0>();  // nothing of the plan prefetch may still be under way towards this CTA's shared memory
   } else {
-    const int g = threadIdx.x / gsize;
-    const int wg = (threadIdx.x - g * gsize) >> 5;  // warp inside the group
-    for (int i = g; i < my_items && !timed_out; i += G) {
+    // Every consumer warp visits every item and takes the units un = warp, warp + n_cons_warps, ...
+    // of its (16-slot tile, head) grid; a warp without a unit hands the stage back at once.
+    const int cw = threadIdx.x >> 5;
+    for (int i = 0; i < my_items && !timed_out; ++i) {
       const int s = i % S;
       const int use = i / S;
       unsigned char* sp = stage0 + (size_t)s * p.stage_bytes;
@@ -519,19 +523,21 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
       const int cpad = slots_of_window(c, 1);
       const int n_mt = (nwin * cpad + 15) >> 4;
       if (cpad <= 16) {
-        // windows of at most 16 voxels: a tile's slots are its keys; one warp per tile, all heads
-        for (int mt = wg; mt < n_mt; mt += kMmaGroupWarps)
-          tile_all_heads<T, HD, kTableSmem, kMask>(rows, p.row_stride, data_bytes, svox, mt * 16, H, C, table_base,
-                                                   tstride, qscale, reinterpret_cast<T*>(p.out), lane);
+        // windows of at most 16 voxels: a tile's slots are its keys
+        for (int un = cw; un < n_mt * H; un += n_cons_warps) {
+          const int h = un / n_mt, mt = un - h * n_mt;
+          tile_head<T, HD, kTableSmem, kMask>(rows, p.row_stride, data_bytes, svox, zero_row, mt * 16, h, C, table_base,
+                                              tstride, qscale, reinterpret_cast<T*>(p.out), lane);
+        }
       } else {
         const int nkb = cpad >> 4;  // 16-key blocks per window
-        for (int un = wg; un < n_mt * H; un += kMmaGroupWarps) {
-          const int mt = un / H, h = un - mt * H;
+        for (int un = cw; un < n_mt * H; un += n_cons_warps) {
+          const int h = un / n_mt, mt = un - h * n_mt;
           const int kbase = (mt * 16 / cpad) * cpad;  // first key slot of the window this tile belongs to
           MmaUnit<HD> u;
           unit_begin<T, HD>(u, rows, p.row_stride, data_bytes, mt * 16, h, lane);
           for (int kb = 0; kb < nkb; ++kb)
-            unit_key_block<T, HD, kTableSmem, kMask>(u, rows, p.row_stride, data_bytes, kbase + kb * 16,
+            unit_key_block<T, HD, kTableSmem, kMask>(u, rows, p.row_stride, data_bytes, zero_row, kbase + kb * 16,
                                                      (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
                                                      table_base, tstride, h, qscale, lane);
           unit_finish<T, HD>(u, svox, mt * 16, h, C, reinterpret_cast<T*>(p.out), lane);
@@ -547,8 +553,8 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
     // Nobody consumes what is still in flight, but the CTA must not retire under copies that
     // target its shared memory: each producer warp waits, bounded, for the last use of every stage
     // it submitted copies to (whether the phase completes or not, the wait outlasts any copy).
-    if (is_producer && lane == 0)
-      for (int j = max(0, issued - S); j < issued; ++j) mbar_wait_bounded(full + j % S, (j / S) & 1);
+    if (is_producer && lane == 0) drain_producer(full, pw, PW, S, issued);
+    if (kTableSmem && threadIdx.x == 0 && !table_ok) mbar_wait_bounded(tbar, 0);
     return;
   }
   if (n_items <= n_small) return;
@@ -636,16 +642,12 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const int slot = (lane + 32 * k) * PW + pw;
-          if (slot < tile) {
-            unsigned char* row = krows + (size_t)slot * p.row_stride;
-            *reinterpret_cast<int2*>(row + data_bytes) =
+          if (slot < tile)
+            *reinterpret_cast<int2*>(krows + (size_t)slot * p.row_stride + data_bytes) =
                 kv[k] >= 0 ? row_meta(kmeta[k], 0, p.rel_off) : pad_meta(p.rel_off);
-            if (kv[k] < 0) zero_v<T>(row, C);  // p = 0 times a stale Inf would be NaN
-          }
         }
         const int my_rows = __popc(__ballot_sync(0xffffffffu, kv[0] >= 0)) + __popc(__ballot_sync(0xffffffffu, kv[1] >= 0));
-        fence_async_smem();  // the zeroed v parts (generic proxy) against later bulk copies onto them
-        __syncwarp();        // every lane's stores before the arrive that releases them
+        __syncwarp();        // every lane's metadata stores before the arrive that releases them
         if (lane == 0) mbar_expect_tx(dfull + s, (uint32_t)my_rows * kv_bytes);
         __syncwarp();
 #pragma unroll
@@ -679,7 +681,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMaxGroups + 32 * kMaxPr
             const unsigned char* krows = stage0 + (size_t)s * p.stage_bytes + kMmaStageRowsOff;
             const int n_k = min(tile, c - kt * tile);
             for (int kb = 0; kb * 16 < n_k; ++kb)
-              unit_key_block<T, HD, kTableSmem, kMask>(u, krows, p.row_stride, data_bytes, kb * 16,
+              unit_key_block<T, HD, kTableSmem, kMask>(u, krows, p.row_stride, data_bytes, zero_row, kb * 16,
                                                        (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
                                                        table_base, tstride, h, qscale, lane);
           }
@@ -711,25 +713,24 @@ static MmaShape mma_shape(int tile, int heads, int head_dim, const int32_t rpb_w
   const int C = heads * head_dim;
   s.row_stride = 3 * C * 2 + 16;  // +16 B: per-row metadata, and consecutive rows fall on different banks
   s.stage_bytes = kMmaStageRowsOff + tile * s.row_stride;
-  // in shared memory the table's rows are padded to a multiple of four heads (one 16-byte load
-  // then brings the biases of four heads)
-  const int tf = (2 * rpb_window[0] - 1) * (2 * rpb_window[1] - 1) * (2 * rpb_window[2] - 1) * ((heads + 3) & ~3);
+  const int tf = (2 * rpb_window[0] - 1) * (2 * rpb_window[1] - 1) * (2 * rpb_window[2] - 1) * heads;
   // The bias table goes to shared memory when four stages still fit beside it (look-ups from global
   // memory cost a dense window about a quarter of its time); otherwise it stays in global memory.
   const size_t budget = size_t(226) * 1024;
   const size_t tbytes = ((size_t)tf * 4 + 15) & ~size_t(15);
-  const bool table_smem = 256 + tbytes + 4 * (size_t)s.stage_bytes <= budget;
+  // Barriers, the row of zeros, the table (when four stages still fit beside it: look-ups from global
+  // memory cost a dense window about a quarter of its time) and, per stage, the stage itself plus the
+  // plan-prefetch rings of its producer warp.
+  const size_t base = 256 + (size_t)s.row_stride;
+  const size_t per_stage = (size_t)s.stage_bytes + producer_scratch_bytes(tile);
+  const bool table_smem = base + tbytes + 4 * per_stage <= budget;
   s.table_floats = table_smem ? tf : 0;
-  const size_t fixed = 256 + (table_smem ? tbytes : 0);
-  int stages = (int)((budget - fixed) / s.stage_bytes);
+  const size_t fixed = base + (table_smem ? tbytes : 0);
+  int stages = (int)((budget - fixed) / per_stage);
   if (stages > kMaxStages) stages = kMaxStages;
-  int groups = stages - 1;
-  if (groups > kMaxGroups) groups = kMaxGroups;
-  if (groups < 1) groups = 1;
-  if (groups > stages) groups = stages;
   s.stages = stages;
-  s.groups = groups;
-  s.smem = fixed + (size_t)(stages > 0 ? stages : 1) * s.stage_bytes;
+  s.groups = kMmaGroups;  // consumer warps = 4 per group; they all work on the same item
+  s.smem = fixed + (size_t)(stages > 0 ? stages : 1) * per_stage;
   return s;
 }
 
@@ -746,7 +747,7 @@ static int launch_mma(AttnParams p, const MmaShape& s, cudaStream_t stream) {
   int dev = 0, sms = 0;
   SSW_CUDA_TRY(cudaGetDevice(&dev));
   SSW_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  p.prod_warps = 4;  // 16-bit rows are short: the copy submission rate, not the bytes, bounds the producer
+  p.prod_warps = s.stages;
   const int threads = p.groups * kMmaGroupWarps * 32 + 32 * p.prod_warps;
   // four variants: bias table in shared memory or not, shift mask or not
   void (*kern)(AttnParams) =
