@@ -38,6 +38,7 @@ struct AttnParams {
   int stage_bytes;    // bytes of one pipeline stage
   int out_off;        // byte offset of the 16-bit output staging area inside a stage (0 for fp32)
   int table_floats;   // > 0: the bias table is staged in shared memory (that many floats)
+  int skip_big;       // tensor-core kernel: windows beyond a pack are left to the tcgen05 kernel
 };
 
 

@@ -807,7 +807,8 @@ static int dispatch(const AttnParams& p, int hd, int threads, size_t smem, cudaS
 }
 
 int mma_default_tile(int heads, int head_dim, const int32_t rpb_window[3]);
-int run_attn_mma(AttnParams p, int dtype, int head_dim, const int32_t rpb_window[3], cudaStream_t stream);
+int run_attn_mma(AttnParams p, int dtype, int head_dim, const int32_t rpb_window[3], const int32_t* bins,
+                 const int32_t* win_start, const int32_t* win_pstart, int n_per_window, cudaStream_t stream);
 
 }  // namespace ssw
 
@@ -864,7 +865,8 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   if (L->padded) {
     // padded plan: the tensor-core kernel takes both the packs and the windows beyond a pack
     if (elt != 2 || attn_vals) return SSW_E_INVALID;
-    return run_attn_mma(p, dtype, head_dim, rpb_window, stream);
+    return run_attn_mma(p, dtype, head_dim, rpb_window, plan + L->off_bins, plan + L->off_win_start,
+                        plan + L->off_win_pstart, (int)L->n_per_window, stream);
   }
   // fp32 without the COO output: the channels of a (row, head) are split over a lane pair
   bool split = dtype == SSW_F32 && !attn_vals && head_dim % 8 == 0;

@@ -557,7 +557,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMmaGroups + 32 * kMaxPr
     if (kTableSmem && threadIdx.x == 0 && !table_ok) mbar_wait_bounded(tbar, 0);
     return;
   }
-  if (n_items <= n_small) return;
+  if (n_items <= n_small || p.skip_big) return;
 
   // ------------------------------------------------------------------------------------------
   // Phase 2: windows with c > tile.  Stage 0 holds the item's query rows (q slices), stages
@@ -759,9 +759,26 @@ static int launch_mma(AttnParams p, const MmaShape& s, cudaStream_t stream) {
   return SSW_OK;
 }
 
+static int run_attn_mma_packs(AttnParams p, int dtype, int head_dim, const int32_t rpb_window[3], cudaStream_t stream);
+
 // Padded plan, 16-bit inputs: packs and larger windows.  `p` arrives with the plan pointers,
 // qkv/out/table, H, C, tile, scale, use_mask and rel_off filled in.
-int run_attn_mma(AttnParams p, int dtype, int head_dim, const int32_t rpb_window[3], cudaStream_t stream) {
+int run_attn_dense(const AttnParams& a, const int32_t* bins, const int32_t* win_start, const int32_t* win_pstart,
+                   int n_per_window, int dtype, const int32_t rpb_window[3], cudaStream_t stream);
+bool attn_dense_supported(int head_dim, int n_per_window, const int32_t rpb_window[3]);
+
+int run_attn_mma(AttnParams p, int dtype, int head_dim, const int32_t rpb_window[3], const int32_t* bins,
+                 const int32_t* win_start, const int32_t* win_pstart, int n_per_window, cudaStream_t stream) {
+  // Windows beyond a pack: the tcgen05 kernel where it serves the shape (and the window size allows
+  // such windows at all), else the second phase of this kernel.
+  const bool dense = n_per_window > p.tile && attn_dense_supported(head_dim, n_per_window, rpb_window);
+  p.skip_big = dense ? 1 : 0;
+  const int st = run_attn_mma_packs(p, dtype, head_dim, rpb_window, stream);
+  if (st != SSW_OK || !dense) return st;
+  return run_attn_dense(p, bins, win_start, win_pstart, n_per_window, dtype, rpb_window, stream);
+}
+
+static int run_attn_mma_packs(AttnParams p, int dtype, int head_dim, const int32_t rpb_window[3], cudaStream_t stream) {
   const MmaShape s = mma_shape(p.tile, p.H, head_dim, rpb_window);
   // three stages at least: the second phase keeps the query tile in one and needs two for key tiles
   if (s.stages < 3 || s.smem > 227 * 1024) return SSW_E_UNSUPPORTED;
