@@ -124,9 +124,9 @@ __device__ __forceinline__ uint32_t f2h2(float a, float b) {  // two floats -> p
 //   K  c_cap x 64    V  c_cap x 64    (64-byte swizzle; key tile j = rows [64 j, 64 j + 64))
 //   Q  2 x 128 x 64  (64-byte swizzle)          P  128 x 128 (128-byte swizzle) twice: P and its bf16 residual
 //   per unit (double buffered): the bias slice of its head, (2Wz-1)(2Wy-1)(2Wx-1) floats
-//   pre-multiplied by log2 e; voxel id and metadata (code | region << 16) per row of its window
+//   pre-multiplied by log2 e; per row of its window the voxel id, 4 x relative-position code, region
 struct DenseSmem {
-  uint32_t k, v, q, p, bias, bias_floats, vox, meta, total;
+  uint32_t k, v, q, p, bias, bias_floats, vox, rel4, reg, total;
 };
 __host__ __device__ inline DenseSmem dense_smem(int c_cap, int table_rows) {
   DenseSmem s;
@@ -138,7 +138,8 @@ __host__ __device__ inline DenseSmem dense_smem(int c_cap, int table_rows) {
   s.bias_floats = ((uint32_t)table_rows + 3u) & ~3u;
   s.bias = o; o += 2u * s.bias_floats * 4u;
   s.vox = o; o += 2u * (uint32_t)c_cap * 4u;
-  s.meta = o; o += 2u * (uint32_t)c_cap * 4u;
+  s.rel4 = o; o += 2u * (uint32_t)c_cap * 4u;
+  s.reg = o; o += 2u * (uint32_t)c_cap * 4u;
   s.total = o;
   return s;
 }
@@ -317,7 +318,8 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
       const int nkt = (c + kDK - 1) / kDK, nqt = (c + kDQ - 1) / kDQ;
       const int mb = un & 1;
       int* wvox = reinterpret_cast<int*>(smem + L.vox) + mb * p.c_cap;
-      int* wmeta = reinterpret_cast<int*>(smem + L.meta) + mb * p.c_cap;
+      int* wrel4 = reinterpret_cast<int*>(smem + L.rel4) + mb * p.c_cap;
+      int* wreg = reinterpret_cast<int*>(smem + L.reg) + mb * p.c_cap;
       // ---- the window's voxel ids and metadata
       if (un >= 2 && !mbar_wait_bounded(meta_empty + mb, ((un >> 1) - 1) & 1)) { timed_out = true; break; }
       for (int r = pw * 32 + lane; r < nkt * kDK; r += kDProd * 32) {  // (rows from c on: neutral entries)
@@ -329,7 +331,8 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
         const bool ok = (unsigned)vx < (unsigned)p.n_vox && meta_rel(m) <= p.rel_off;
         if (!ok) atomicOr(reinterpret_cast<unsigned*>(p.header + SSW_H_ERROR), SSW_DEV_BAD_PLAN);
         wvox[r] = ok ? vx : 0;
-        wmeta[r] = ok ? (meta_rel(m) | (meta_region(m) << 16)) : 0;
+        wrel4[r] = ok ? meta_rel(m) * 4 : 0;
+        wreg[r] = ok ? meta_region(m) : 0;
       }
       // ---- the head's bias slice (rows of the table are [code][head])
       {
@@ -383,15 +386,16 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
       const int nkt = (c + kDK - 1) / kDK, nqt = (c + kDQ - 1) / kDQ;
       const int mb = un & 1;
       const int* wvox = reinterpret_cast<const int*>(smem + L.vox) + mb * p.c_cap;
-      const int* wmeta = reinterpret_cast<const int*>(smem + L.meta) + mb * p.c_cap;
-      const float* bias_s = reinterpret_cast<const float*>(smem + L.bias) + (size_t)mb * L.bias_floats;
+      const int* wrel4 = reinterpret_cast<const int*>(smem + L.rel4) + mb * p.c_cap;
+      const int* wreg = reinterpret_cast<const int*>(smem + L.reg) + mb * p.c_cap;
+      const unsigned char* bias_s = smem + L.bias + (size_t)mb * L.bias_floats * 4;
       if (!mbar_wait_bounded(meta_full + mb, (un >> 1) & 1)) { timed_out = true; break; }
       for (int t = 0; t < nqt && !timed_out; ++t) {
         const int qrow = t * kDQ + row_in_tile;
         const bool live = qrow < c;
-        const int my_meta = live ? wmeta[qrow] : 0;
-        const float* my_bias = bias_s + (my_meta & 0xffff) + p.rel_off;
-        const int my_region = my_meta >> 16;
+        // bias of (me, key j) = slice[(code_me + rel_off) - code_j]: my row's base, minus 4 * code_j
+        const unsigned char* my_bias = bias_s + (live ? wrel4[qrow] : 0) + p.rel_off * 4;
+        const int my_region = live ? wreg[qrow] : 0;
         float m = 0.f, l = 0.f, corr_prev = 1.f;   // the maximum starts from 0 (ops.cu:137)
         float o[kDHD];
 #pragma unroll
@@ -412,53 +416,56 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
             // scores in the log2 domain: bias from the head's slice, -100 across regions, -inf beyond c
             float s[kDK];
             float mx = -INFINITY;
-            const int4* km4 = reinterpret_cast<const int4*>(wmeta + j * kDK);
+            const int4* r4 = reinterpret_cast<const int4*>(wrel4 + j * kDK);
+            const int4* g4 = reinterpret_cast<const int4*>(wreg + j * kDK);
 #pragma unroll
             for (int q4 = 0; q4 < kDK / 4; ++q4) {
-              const int4 km = km4[q4];
-              const int kmv[4] = {km.x, km.y, km.z, km.w};
+              const int4 kr = r4[q4];
+              const int krv[4] = {kr.x, kr.y, kr.z, kr.w};
+              int kgv[4] = {0, 0, 0, 0};
+              if constexpr (kMask) {
+                const int4 kg = g4[q4];
+                kgv[0] = kg.x; kgv[1] = kg.y; kgv[2] = kg.z; kgv[3] = kg.w;
+              }
 #pragma unroll
               for (int x = 0; x < 4; ++x) {
                 const int jj = q4 * 4 + x;
-                float v = fmaf(__uint_as_float(sr[jj >> 5][jj & 31]), qscale, my_bias[-(kmv[x] & 0xffff)]);
-                if (kMask && (kmv[x] >> 16) != my_region) v += -100.0f * kLog2e;
-                v = jj < nk ? v : -INFINITY;
+                float v = fmaf(__uint_as_float(sr[jj >> 5][jj & 31]), qscale, *reinterpret_cast<const float*>(my_bias - krv[x]));
+                if (kMask && kgv[x] != my_region) v += -100.0f * kLog2e;
                 s[jj] = v;
-                mx = fmaxf(mx, v);
               }
             }
+            if (nk < kDK) {  // the window's last key tile: nothing beyond its last voxel
+#pragma unroll
+              for (int jj = 0; jj < kDK; ++jj) s[jj] = jj < nk ? s[jj] : -INFINITY;
+            }
+#pragma unroll
+            for (int jj = 0; jj < kDK; ++jj) mx = fmaxf(mx, s[jj]);
             const float m_new = fmaxf(m, mx);
             const float corr = fast_exp2(m - m_new);
             m = m_new;
-            float sum = 0.f;
-            uint32_t ph[kDK / 2];
-#pragma unroll
-            for (int jj = 0; jj < kDK; jj += 2) {
-              const float p0 = fast_exp2(s[jj] - m), p1 = fast_exp2(s[jj + 1] - m);
-              sum += p0 + p1;
-              ph[jj >> 1] = pack2<T>(p0, p1);
-              if constexpr (kSplitP) {  // keep the residuals where the scores were
-                s[jj] = p0 - __uint_as_float(ph[jj >> 1] << 16);
-                s[jj + 1] = p1 - __uint_as_float(ph[jj >> 1] & 0xffff0000u);
-              }
-            }
-            l = l * corr + sum;
             // The one P buffer was last read by the P V of the tile before; the same completion says
             // that tile's O_part is in tensor memory.
             const uint32_t gp = g - 1, bp = gp & 1;
             if (g >= 1 && !mbar_wait_bounded(pv_done + bp, (gp >> 1) & 1)) { timed_out = true; break; }
             unsigned char* prow = smem + L.p + (size_t)row_in_tile * 128;
+            float sum = 0.f;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-              *reinterpret_cast<uint4*>(prow + ((ch ^ (row_in_tile & 7)) << 4)) =
-                  make_uint4(ph[4 * ch], ph[4 * ch + 1], ph[4 * ch + 2], ph[4 * ch + 3]);
-            if constexpr (kSplitP) {
+            for (int ch = 0; ch < kDK / 8; ++ch) {
+              uint32_t hi[4], lo[4];
 #pragma unroll
-              for (int ch = 0; ch < 8; ++ch)
-                *reinterpret_cast<uint4*>(prow + kDQ * 128 + ((ch ^ (row_in_tile & 7)) << 4)) =
-                    make_uint4(pack2<T>(s[8 * ch], s[8 * ch + 1]), pack2<T>(s[8 * ch + 2], s[8 * ch + 3]),
-                               pack2<T>(s[8 * ch + 4], s[8 * ch + 5]), pack2<T>(s[8 * ch + 6], s[8 * ch + 7]));
+              for (int x = 0; x < 4; ++x) {
+                const float p0 = fast_exp2(s[8 * ch + 2 * x] - m), p1 = fast_exp2(s[8 * ch + 2 * x + 1] - m);
+                sum += p0 + p1;
+                hi[x] = pack2<T>(p0, p1);
+                if constexpr (kSplitP)
+                  lo[x] = pack2<T>(p0 - __uint_as_float(hi[x] << 16), p1 - __uint_as_float(hi[x] & 0xffff0000u));
+              }
+              *reinterpret_cast<uint4*>(prow + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+              if constexpr (kSplitP)
+                *reinterpret_cast<uint4*>(prow + kDQ * 128 + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             }
+            l = l * corr + sum;
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + b);
