@@ -19,10 +19,13 @@
 //   O_part[128 x 32] = P V_tile          tcgen05.mma, added into fp32 registers by the row's thread
 //                  with the correction factor of the running maximum
 //
-// Warp roles (256 threads, one CTA per SM): warp 0 issues the MMAs (one elected lane) and owns the
+// Warp roles (384 threads, one CTA per SM): warp 0 issues the MMAs (one elected lane) and owns the
 // tensor-memory allocation; warps 1-3 gather rows (plain 16-byte loads by voxel id, stored with the
-// 64-byte swizzle the operand descriptors name); warps 4-7 are the softmax rows (a warp may touch
-// the 32 tensor-memory lanes warp_id % 4 selects).  Everything is handed over through mbarriers
+// 64-byte swizzle the operand descriptors name); warps 4-11 are the softmax rows: a warp may touch
+// the 32 tensor-memory lanes warp_id % 4 selects, so two warps share each quarter of the query
+// rows, one for the first 32 keys of a tile and the first 16 output channels, one for the rest
+// (they exchange their partial row maxima per tile and their row sums per query tile through shared
+// memory): two warps per scheduler instead of one.  Everything is handed over through mbarriers
 // with bounded waits; on expiry the kernel sets SSW_DEV_TIMEOUT, lets the tensor cores drain and
 // frees its tensor memory before it returns.
 #include <math.h>
@@ -37,7 +40,8 @@ constexpr int kDHD = 32;       // head_dim
 constexpr int kDRowB = 64;     // bytes of one q / k / v head slice (32 x 16 bit)
 constexpr int kDMaxKT = 16;    // key tiles per window at most (1024 keys)
 constexpr int kDProd = 3;      // producer warps
-constexpr int kDThreads = 256;
+constexpr int kDThreads = 384;
+constexpr int kDHalf = kDK / 2;  // keys of a tile one softmax thread looks after
 constexpr int kTmemCols = 256; // S: 2 x 64 columns, O_part: 2 x 32 columns
 constexpr int kTmemS = 0, kTmemO = 128;
 
@@ -94,6 +98,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory operand descriptor (version 1): start address, leading / stride byte offsets in
@@ -114,6 +126,22 @@ __device__ __forceinline__ uint32_t instr_desc(int a_fmt, int b_fmt, int b_mn_ma
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kDQ >> 4) << 24);
 }
 
+// shared-memory accesses by 32-bit shared address (the softmax loop does one bias look-up per
+// score: address arithmetic in 32 bits and loads that are certain to take the shared-memory path)
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ int4 lds_v4(uint32_t a) {
+  int4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts_v4(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+
 __device__ __forceinline__ uint32_t f2h2(float a, float b) {  // two floats -> packed fp16 pair
   __half2 v = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -121,6 +149,7 @@ __device__ __forceinline__ uint32_t f2h2(float a, float b) {  // two floats -> p
 
 // Shared memory (byte offsets from a 1024-byte aligned base):
 //   [0, 1024)        mbarriers and the tensor-memory address
+//   [1024, 3072)     partial row maxima / sums the two softmax threads of a row exchange
 //   K  c_cap x 64    V  c_cap x 64    (64-byte swizzle; key tile j = rows [64 j, 64 j + 64))
 //   Q  2 x 128 x 64  (64-byte swizzle)          P  128 x 128 (128-byte swizzle) twice: P and its bf16 residual
 //   per unit (double buffered): the bias slice of its head, (2Wz-1)(2Wy-1)(2Wx-1) floats
@@ -130,7 +159,7 @@ struct DenseSmem {
 };
 __host__ __device__ inline DenseSmem dense_smem(int c_cap, int table_rows) {
   DenseSmem s;
-  uint32_t o = 1024;
+  uint32_t o = 3072;
   s.k = o; o += (uint32_t)c_cap * kDRowB;
   s.v = o; o += (uint32_t)c_cap * kDRowB;
   s.q = o; o += 2u * kDQ * kDRowB;
@@ -163,7 +192,9 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
   uint64_t* meta_full = o_empty + 2;           // [2] a unit's header: voxel ids, metadata, bias slice of its head
   uint64_t* meta_empty = meta_full + 2;        // [2]
   uint64_t* drain_bar = meta_empty + 2;        // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
+  uint64_t* xbar = drain_bar + 1;              // [4] the two warps of a row quarter have posted their partial values
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 4);
+  float* xch = reinterpret_cast<float*>(smem + 1024);  // [2 buffers][2 halves][128 rows] partial maxima / sums
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = p.H, C = p.C;
 
@@ -176,13 +207,14 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
       mbar_init(q_full + b, kDProd);
       mbar_init(q_empty + b, 1);
       mbar_init(s_full + b, 1);
-      mbar_init(s_empty + b, 4);
-      mbar_init(p_full + b, 4);
+      mbar_init(s_empty + b, 8);
+      mbar_init(p_full + b, 8);
       mbar_init(pv_done + b, 1);
-      mbar_init(o_empty + b, 4);
+      mbar_init(o_empty + b, 8);
       mbar_init(meta_full + b, kDProd);
-      mbar_init(meta_empty + b, 4);
+      mbar_init(meta_empty + b, 8);
     }
+    for (int x = 0; x < 4; ++x) mbar_init(xbar + x, 2);
     mbar_init(drain_bar, 1);
     mbar_fence_init();
   }
@@ -374,12 +406,25 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
     }
   } else {
     // =========================================== softmax rows =================================
-    const int sw = warp - 4;                   // tensor-memory lanes [32 sw, 32 sw + 32)
+    const int half = (warp - 4) >> 2;          // which 32 keys of a tile / which 16 output channels
+    const int sw = warp & 3;                   // tensor-memory lanes [32 sw, 32 sw + 32)
     const int row_in_tile = sw * 32 + lane;
     const uint32_t t_lane = (uint32_t)(sw * 32) << 16;
     const float qscale = p.scale * kLog2e;
-    uint32_t g = 0;
+    uint32_t g = 0;    // key tiles so far
+    uint32_t xn = 0;   // exchanges with the partner warp so far
     int un = 0;
+    // post a value for the partner thread (same row, other half) and fetch its value
+    auto exchange = [&](float mine, float& theirs) -> bool {
+      float* slot = xch + (xn & 1) * 256;
+      slot[half * 128 + row_in_tile] = mine;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xbar + sw);
+      const bool ok = mbar_wait_bounded(xbar + sw, xn & 1);
+      theirs = slot[(half ^ 1) * 128 + row_in_tile];
+      ++xn;
+      return ok;
+    };
     for (int u = blockIdx.x; u < n_units && !timed_out; u += gridDim.x, ++un) {
       int first, c, h;
       unit_window(u, first, c, h);
@@ -388,124 +433,130 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
       const int* wvox = reinterpret_cast<const int*>(smem + L.vox) + mb * p.c_cap;
       const int* wrel4 = reinterpret_cast<const int*>(smem + L.rel4) + mb * p.c_cap;
       const int* wreg = reinterpret_cast<const int*>(smem + L.reg) + mb * p.c_cap;
-      const unsigned char* bias_s = smem + L.bias + (size_t)mb * L.bias_floats * 4;
+      const uint32_t bias_a = smem_u32(smem + L.bias) + (uint32_t)mb * L.bias_floats * 4u;
+      const uint32_t rel4_a = smem_u32(wrel4) + half * kDHalf * 4, reg_a = smem_u32(wreg) + half * kDHalf * 4;
       if (!mbar_wait_bounded(meta_full + mb, (un >> 1) & 1)) { timed_out = true; break; }
       for (int t = 0; t < nqt && !timed_out; ++t) {
         const int qrow = t * kDQ + row_in_tile;
         const bool live = qrow < c;
         // bias of (me, key j) = slice[(code_me + rel_off) - code_j]: my row's base, minus 4 * code_j
-        const unsigned char* my_bias = bias_s + (live ? wrel4[qrow] : 0) + p.rel_off * 4;
+        const uint32_t my_bias = bias_a + (uint32_t)(live ? wrel4[qrow] : 0) + (uint32_t)p.rel_off * 4u;
         const int my_region = live ? wreg[qrow] : 0;
         float m = 0.f, l = 0.f, corr_prev = 1.f;   // the maximum starts from 0 (ops.cu:137)
-        float o[kDHD];
+        float o[kDHD / 2];
 #pragma unroll
-        for (int e = 0; e < kDHD; ++e) o[e] = 0.f;
+        for (int e = 0; e < kDHD / 2; ++e) o[e] = 0.f;
         for (int j = 0; j <= nkt && !timed_out; ++j) {
+          const uint32_t gp = g - 1, bp = gp & 1;
           if (j < nkt) {
             const uint32_t b = g & 1;
-            const int nk = min(kDK, c - j * kDK);
+            const int nk = min(kDK, c - j * kDK) - half * kDHalf;  // valid keys among this thread's 32
             if (!mbar_wait_bounded(s_full + b, (g >> 1) & 1)) { timed_out = true; break; }
             tc_fence_after();
-            uint32_t sr[2][32];
-            tmem_ld32(tmem + t_lane + kTmemS + b * kDK, sr[0]);
-            tmem_ld32(tmem + t_lane + kTmemS + b * kDK + 32, sr[1]);
+            uint32_t sr[32];
+            tmem_ld32(tmem + t_lane + kTmemS + b * kDK + half * kDHalf, sr);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty + b);
             // scores in the log2 domain: bias from the head's slice, -100 across regions, -inf beyond c
-            float s[kDK];
-            float mx = -INFINITY;
-            const int4* r4 = reinterpret_cast<const int4*>(wrel4 + j * kDK);
-            const int4* g4 = reinterpret_cast<const int4*>(wreg + j * kDK);
+            float s[kDHalf];
 #pragma unroll
-            for (int q4 = 0; q4 < kDK / 4; ++q4) {
-              const int4 kr = r4[q4];
+            for (int q4 = 0; q4 < kDHalf / 4; ++q4) {
+              const int4 kr = lds_v4(rel4_a + (uint32_t)(j * kDK + q4 * 4) * 4u);
               const int krv[4] = {kr.x, kr.y, kr.z, kr.w};
               int kgv[4] = {0, 0, 0, 0};
               if constexpr (kMask) {
-                const int4 kg = g4[q4];
+                const int4 kg = lds_v4(reg_a + (uint32_t)(j * kDK + q4 * 4) * 4u);
                 kgv[0] = kg.x; kgv[1] = kg.y; kgv[2] = kg.z; kgv[3] = kg.w;
               }
 #pragma unroll
               for (int x = 0; x < 4; ++x) {
                 const int jj = q4 * 4 + x;
-                float v = fmaf(__uint_as_float(sr[jj >> 5][jj & 31]), qscale, *reinterpret_cast<const float*>(my_bias - krv[x]));
+                float v = fmaf(__uint_as_float(sr[jj]), qscale, lds_f32(my_bias - (uint32_t)krv[x]));
                 if (kMask && kgv[x] != my_region) v += -100.0f * kLog2e;
                 s[jj] = v;
               }
             }
-            if (nk < kDK) {  // the window's last key tile: nothing beyond its last voxel
+            if (nk < kDHalf) {  // the window's last key tile: nothing beyond its last voxel
 #pragma unroll
-              for (int jj = 0; jj < kDK; ++jj) s[jj] = jj < nk ? s[jj] : -INFINITY;
+              for (int jj = 0; jj < kDHalf; ++jj) s[jj] = jj < nk ? s[jj] : -INFINITY;
             }
+            float mx;
+            {  // four interleaved partial maxima keep the dependency chain short
+              float m4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-            for (int jj = 0; jj < kDK; ++jj) mx = fmaxf(mx, s[jj]);
-            const float m_new = fmaxf(m, mx);
+              for (int jj = 4; jj < kDHalf; ++jj) m4[jj & 3] = fmaxf(m4[jj & 3], s[jj]);
+              mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            }
+            float mx_other;
+            if (!exchange(mx, mx_other)) { timed_out = true; break; }
+            const float m_new = fmaxf(m, fmaxf(mx, mx_other));
             const float corr = fast_exp2(m - m_new);
             m = m_new;
             // The one P buffer was last read by the P V of the tile before; the same completion says
             // that tile's O_part is in tensor memory.
-            const uint32_t gp = g - 1, bp = gp & 1;
             if (g >= 1 && !mbar_wait_bounded(pv_done + bp, (gp >> 1) & 1)) { timed_out = true; break; }
-            unsigned char* prow = smem + L.p + (size_t)row_in_tile * 128;
-            float sum = 0.f;
+            const uint32_t prow = smem_u32(smem + L.p) + (uint32_t)row_in_tile * 128u;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};  // partial row sums, one per pair position
 #pragma unroll
-            for (int ch = 0; ch < kDK / 8; ++ch) {
+            for (int ch = 0; ch < kDHalf / 8; ++ch) {
               uint32_t hi[4], lo[4];
 #pragma unroll
               for (int x = 0; x < 4; ++x) {
                 const float p0 = fast_exp2(s[8 * ch + 2 * x] - m), p1 = fast_exp2(s[8 * ch + 2 * x + 1] - m);
-                sum += p0 + p1;
+                sum4[x] += p0 + p1;
                 hi[x] = pack2<T>(p0, p1);
                 if constexpr (kSplitP)
                   lo[x] = pack2<T>(p0 - __uint_as_float(hi[x] << 16), p1 - __uint_as_float(hi[x] & 0xffff0000u));
               }
-              *reinterpret_cast<uint4*>(prow + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-              if constexpr (kSplitP)
-                *reinterpret_cast<uint4*>(prow + kDQ * 128 + ((ch ^ (row_in_tile & 7)) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+              const int chg = half * (kDHalf / 8) + ch;  // 16-byte chunk of the tile's 128-byte row
+              sts_v4(prow + ((chg ^ (row_in_tile & 7)) << 4), hi[0], hi[1], hi[2], hi[3]);
+              if constexpr (kSplitP) sts_v4(prow + kDQ * 128 + ((chg ^ (row_in_tile & 7)) << 4), lo[0], lo[1], lo[2], lo[3]);
             }
-            l = l * corr + sum;
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + b);
             // fold the previous tile's O_part in with the factor its maximum update gave
             if (j > 0) {
               tc_fence_after();
-              uint32_t orr[32];
-              tmem_ld32(tmem + t_lane + kTmemO + bp * kDHD, orr);
+              uint32_t orr[16];
+              tmem_ld16(tmem + t_lane + kTmemO + bp * kDHD + half * (kDHD / 2), orr);
               tmem_ld_wait();
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(o_empty + bp);
 #pragma unroll
-              for (int e = 0; e < kDHD; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(orr[e]));
+              for (int e = 0; e < kDHD / 2; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(orr[e]));
             }
             corr_prev = corr;
             ++g;
           } else {
-            const uint32_t gp = g - 1, bp = gp & 1;
             if (!mbar_wait_bounded(pv_done + bp, (gp >> 1) & 1)) { timed_out = true; break; }
             tc_fence_after();
-            uint32_t orr[32];
-            tmem_ld32(tmem + t_lane + kTmemO + bp * kDHD, orr);
+            uint32_t orr[16];
+            tmem_ld16(tmem + t_lane + kTmemO + bp * kDHD + half * (kDHD / 2), orr);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(o_empty + bp);
 #pragma unroll
-            for (int e = 0; e < kDHD; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(orr[e]));
+            for (int e = 0; e < kDHD / 2; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(orr[e]));
           }
         }
+        // the row's sum is the two halves' sums (both were kept relative to the same running maximum)
+        float l_other = 0.f;
+        if (!timed_out && !exchange(l, l_other)) timed_out = true;
         if (live && !timed_out) {
-          const float inv = __frcp_rn(l + 1e-8f);  // ops.cu:164
-          T* dst = reinterpret_cast<T*>(p.out) + (int64_t)wvox[qrow] * C + h * kDHD;
+          const float inv = __frcp_rn(l + l_other + 1e-8f);  // ops.cu:164
+          T* dst = reinterpret_cast<T*>(p.out) + (int64_t)wvox[qrow] * C + h * kDHD + half * (kDHD / 2);
 #pragma unroll
-          for (int e = 0; e < kDHD / 8; ++e) {
-            uint32_t w[4];
+          for (int e = 0; e < kDHD / 16; ++e) {
+            uint32_t ww[4];
 #pragma unroll
-            for (int x = 0; x < 4; ++x) w[x] = pack2<T>(o[8 * e + 2 * x] * inv, o[8 * e + 2 * x + 1] * inv);
-            reinterpret_cast<uint4*>(dst)[e] = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int x = 0; x < 4; ++x) ww[x] = pack2<T>(o[8 * e + 2 * x] * inv, o[8 * e + 2 * x + 1] * inv);
+            reinterpret_cast<uint4*>(dst)[e] = make_uint4(ww[0], ww[1], ww[2], ww[3]);
           }
         }
       }
