@@ -67,20 +67,28 @@ def test_captured_step_keeps_full_join_and_legal_programmatic_edges(dtype):
     for a, b, kind, _, _ in edges:
         if kind == "programmatic":
             assert any(k in b for k in WAITING_KERNELS), f"programmatic edge into {b}"
-    # Two attention nodes.  The first has one predecessor, its own plan's last bucketing kernel.  The
-    # second has two: the first attention call (same stream) and the side stream's last bucketing
-    # kernel.  A launch that carries the programmatic-serialization attribute turns ALL its kernel
+    # Two attention calls.  Each starts with k_attn_fused or k_attn_mma; for 16-bit inputs of head_dim
+    # 32 the kernel for windows beyond a pack (k_attn_dense) is chained behind k_attn_mma.  The
+    # first call has one predecessor, its own plan's last bucketing kernel.  The second has two: the
+    # last kernel of the first call (same stream) and the side stream's last bucketing kernel.  A
+    # launch that carries the programmatic-serialization attribute turns ALL its kernel
     # predecessors into programmatic edges, the cross-stream one included; what makes that safe is
     # the rule checked above (the target waits for every prerequisite grid before its first read).
-    attn_nodes = sorted({e[1] for e in edges if "k_attn" in e[1]}, key=lambda n: int(n.split(":")[0]))
-    assert len(attn_nodes) == 2
-    incoming = {n: [e for e in edges if e[1] == n] for n in attn_nodes}
-    second = [n for n in attn_nodes if len(incoming[n]) == 2]
-    first = [n for n in attn_nodes if len(incoming[n]) == 1]
+    def first_kernel(name):
+        return "k_attn_fused" in name or "k_attn_mma" in name
+
+    heads = sorted({e[1] for e in edges if first_kernel(e[1])}, key=lambda n: int(n.split(":")[0]))
+    assert len(heads) == 2
+    incoming = {n: [e for e in edges if e[1] == n] for n in heads}
+    second = [n for n in heads if len(incoming[n]) == 2]
+    first = [n for n in heads if len(incoming[n]) == 1]
     assert len(second) == 1 and len(first) == 1
     assert "k_scatter" in incoming[first[0]][0][0]
     assert sum("k_scatter" in e[0] for e in incoming[second[0]]) == 1      # the join with the side stream
-    assert any(e[0] == first[0] for e in incoming[second[0]])               # and the stream's own order
+    assert sum("k_attn" in e[0] for e in incoming[second[0]]) == 1         # and the stream's own order
+    for n in {e[1] for e in edges if "k_attn_dense" in e[1]}:               # chained behind its k_attn_mma
+        inc = [e for e in edges if e[1] == n]
+        assert len(inc) == 1 and "k_attn_mma" in inc[0][0]
     # nothing but kernels of one call's chain and memsets in front of them: the first kernel of a
     # chain is an ordinary launch, fully ordered behind the clears
     for a, b, kind, _, _ in edges:
