@@ -153,6 +153,17 @@ int ssw_bucket_windows(const int32_t* coords, const ssw_geometry* geom,
                        const int32_t rpb_window[3],
                        const ssw_plan_layout* L, int32_t* plan, int32_t* scratch, void* stream);
 
+/* ssw_bucket_windows restricted to the voxels whose window id (as ssw_window_keys gives it) lies
+ * in [win_lo, win_hi): the others are skipped without error, their inv_perm entries stay
+ * unwritten, and header[SSW_H_N] counts the voxels taken.  Voxel ids in the plan still refer to the
+ * caller's full arrays.  This is the shard of one scene a GPU works on when the scene is split by
+ * contiguous window ranges (windows never interact: ops.cu:359-377 computes block by block). */
+int ssw_bucket_windows_range(const int32_t* coords, const ssw_geometry* geom,
+                             const int32_t* indices, const int8_t* mask, int32_t mask_windows,
+                             const int32_t rpb_window[3],
+                             const ssw_plan_layout* L, int32_t* plan, int32_t* scratch,
+                             int32_t win_lo, int32_t win_hi, void* stream);
+
 /* No counterpart in upstream.  ssw_bucket_windows for callers that cannot hand over scratch memory:
  * hosts that embed this library inside another framework's memory plan, or run under a runtime
  * that forbids device allocation once it has started, have no buffer to pass as `scratch`.  The
@@ -193,6 +204,21 @@ int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t head_dim,
                    const ssw_plan_layout* L, const int32_t* plan,
                    const float* table, const int32_t rpb_window[3], float scale, int use_mask,
                    void* out, void* attn_vals, void* stream);
+
+/* ssw_attn_fused with several destination buffers: every finished output row is stored to
+ * outs[0..n_outs-1] (1 <= n_outs <= 8), each an [N, heads*head_dim] buffer of `dtype`.  outs[0] is
+ * the caller's own; the others are the same buffer on peer GPUs of the node, mapped into this
+ * process (CUDA IPC) with peer access enabled: this is how one scene split over several GPUs by
+ * window ranges ends with the complete output on every GPU and no gather step - plain stores over
+ * NVLink from the kernel's epilogue.  Upstream has no multi-GPU path (it relies on its trainer's
+ * data parallelism); the single-destination semantics are those of ssw_attn_fused. */
+int ssw_attn_fused_multi(const void* qkv, int dtype, int32_t heads, int32_t head_dim,
+                         const ssw_plan_layout* L, const int32_t* plan,
+                         const float* table, const int32_t rpb_window[3], float scale, int use_mask,
+                         void* const* outs, int32_t n_outs, void* attn_vals, void* stream);
+/* Host only: lets kernels on the current device store to memory of `peer_device` (cudaDeviceEnablePeerAccess;
+ * "already enabled" is not an error).  SSW_E_UNSUPPORTED when the two devices cannot reach each other. */
+int ssw_enable_peer_access(int32_t peer_device);
 
 /* Backward of ssw_attn_fused: gradients of qkv and of the bias table from the gradient of `out`,
  * with the probabilities recomputed instead of stored.  It replaces what upstream's autograd runs

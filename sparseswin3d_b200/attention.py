@@ -66,7 +66,8 @@ def default_tile_rows(num_heads: int, head_dim: int, dtype: torch.dtype, rpb_win
 
 
 def window_attention_fused(qkv: torch.Tensor, plan: WindowPlan, table: torch.Tensor, scale: float,
-                           use_mask: bool = False, return_attn: bool = False, out: Optional[torch.Tensor] = None):
+                           use_mask: bool = False, return_attn: bool = False, out: Optional[torch.Tensor] = None,
+                           peer_out_ptrs: Sequence[int] = ()):
     """Everything between the two Linear layers of WindowAttentionSparse.forward
     (swin3d_base.py:659-675) in one kernel launch.
 
@@ -75,7 +76,11 @@ def window_attention_fused(qkv: torch.Tensor, plan: WindowPlan, table: torch.Ten
     table  relative_position_bias_table [(2Wz-1)(2Wy-1)(2Wx-1), H]
     Returns out [N, H*hd] in the caller's voxel order; with return_attn=True also the post-softmax
     COO values in upstream order (window, head, pos_i, pos_j) — that variant synchronises once to
-    size the buffer."""
+    size the buffer.
+
+    ``peer_out_ptrs``: device addresses of the same [N, H*hd] buffer on peer GPUs (mapped into this
+    process, peer access enabled; at most seven): every finished row is stored there as well as to
+    ``out`` (see ``shard.PeerRows``)."""
     if not qkv.is_cuda:
         raise _lib.SswError("qkv must be a CUDA tensor (there is no CPU path)")
     if qkv.dim() != 4 or qkv.shape[1] != 3:
@@ -106,8 +111,10 @@ def window_attention_fused(qkv: torch.Tensor, plan: WindowPlan, table: torch.Ten
             raise _lib.SswError("sum c^2 * heads leaves the int32 domain of the COO layout")
         attn = torch.empty(st["sum_c2"] * H, dtype=qkv.dtype, device=qkv.device)
     rwc = (_lib.i32 * 3)(*rw)
-    check(lib.ssw_attn_fused(ptr(qkv), dtype_code(qkv.dtype), H, hd, plan.layout, ptr(plan.plan), ptr(table), rwc,
-                             float(scale), int(bool(use_mask)), ptr(out), ptr(attn), stream_ptr(qkv.device)),
+    dests = [ptr(out)] + [int(a) for a in peer_out_ptrs]
+    outs = (_lib.vp * len(dests))(*dests)
+    check(lib.ssw_attn_fused_multi(ptr(qkv), dtype_code(qkv.dtype), H, hd, plan.layout, ptr(plan.plan), ptr(table), rwc,
+                                   float(scale), int(bool(use_mask)), outs, len(dests), ptr(attn), stream_ptr(qkv.device)),
           "ssw_attn_fused")
     return (out, attn) if return_attn else out
 

@@ -14,9 +14,19 @@ constexpr int kMaxStages = 6;
 constexpr int kMaxGroups = 4;
 constexpr int kMaxTile = 64, kMaxProducerWarps = kMaxStages;
 
+// Destinations of the output rows: the caller's buffer and, when one scene is split over several
+// GPUs, the same [N, C] buffer on every peer (mapped into this process): a finished row is stored
+// to all of them with ordinary stores, so no gather step follows the kernel.
+constexpr int kMaxOuts = 8;
+struct OutSet {
+  void* base[kMaxOuts];
+  int n;
+};
+
 struct AttnParams {
   const void* qkv;
-  void* out;
+  void* out;          // = outs.base[0]
+  OutSet outs;
   void* attn_vals;
   int32_t* header;
   const int4* pack_desc;

@@ -47,7 +47,7 @@ constexpr int kTmemS = 0, kTmemO = 128;
 
 struct DenseParams {
   const void* qkv;
-  void* out;
+  OutSet outs;
   int32_t* header;
   const int32_t* bins;        // per-occupancy tables of the plan
   const int32_t* pack_win;
@@ -550,13 +550,14 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
         if (!timed_out && !exchange(l, l_other)) timed_out = true;
         if (live && !timed_out) {
           const float inv = __frcp_rn(l + l_other + 1e-8f);  // ops.cu:164
-          T* dst = reinterpret_cast<T*>(p.out) + (int64_t)wvox[qrow] * C + h * kDHD + half * (kDHD / 2);
+          const int64_t off = (int64_t)wvox[qrow] * C + h * kDHD + half * (kDHD / 2);
 #pragma unroll
           for (int e = 0; e < kDHD / 16; ++e) {
             uint32_t ww[4];
 #pragma unroll
             for (int x = 0; x < 4; ++x) ww[x] = pack2<T>(o[8 * e + 2 * x] * inv, o[8 * e + 2 * x + 1] * inv);
-            reinterpret_cast<uint4*>(dst)[e] = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+            for (int d = 0; d < p.outs.n; ++d)
+              reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.outs.base[d]) + off)[e] = make_uint4(ww[0], ww[1], ww[2], ww[3]);
           }
         }
       }
@@ -574,7 +575,7 @@ int run_attn_dense(const AttnParams& a, const int32_t* bins, const int32_t* win_
                    int n_per_window, int dtype, const int32_t rpb_window[3], cudaStream_t stream) {
   DenseParams p = {};
   p.qkv = a.qkv;
-  p.out = a.out;
+  p.outs = a.outs;
   p.header = a.header;
   p.bins = bins;
   p.pack_win = a.pack_win;

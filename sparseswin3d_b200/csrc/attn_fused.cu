@@ -549,8 +549,9 @@ __global__ void __maxnreg__(regs_for_threads(MAXT)) k_attn_fused(AttnParams p) {
             else
               attend_keys_split<HH, kTableSmem, false>(hs, rows, p.row_stride, data_bytes, kbeg, c,
                                                        (C + h * HD + x * HH) * 4, C, table_h, 0, lanes);
-            store_out<T, HH>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD + x * HH, hs,
-                             1.0f / (hs.l + 1e-8f));
+            for (int d = 0; d < p.outs.n; ++d)
+              store_out<T, HH>(reinterpret_cast<T*>(p.outs.base[d]) + (int64_t)my_vox * C + h * HD + x * HH, hs,
+                               1.0f / (hs.l + 1e-8f));
           }
         }
         __syncwarp();
@@ -583,7 +584,8 @@ __global__ void __maxnreg__(regs_for_threads(MAXT)) k_attn_fused(AttnParams p) {
           }
           // Straight to global memory: each thread owns a 16-byte-aligned run of HD outputs of one
           // row (bulk stores of whole rows were tried; one bulk operation per row is what bounds them).
-          store_out<T, HD>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD, st, inv_l);
+          for (int d = 0; d < p.outs.n; ++d)
+            store_out<T, HD>(reinterpret_cast<T*>(p.outs.base[d]) + (int64_t)my_vox * C + h * HD, st, inv_l);
         }
       }
       // widen_rows wrote the stage through the generic proxy; the next bulk copy into it goes
@@ -711,7 +713,8 @@ __global__ void __maxnreg__(regs_for_threads(MAXT)) k_attn_fused(AttnParams p) {
         __syncthreads();  // everyone done with this tile before it is overwritten
       }
       if (row_active)
-        store_out<T, HB>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD + xh * HB, st, inv_l);
+        for (int d = 0; d < p.outs.n; ++d)
+          store_out<T, HB>(reinterpret_cast<T*>(p.outs.base[d]) + (int64_t)my_vox * C + h * HD + xh * HB, st, inv_l);
     }
   }
 }
@@ -830,9 +833,21 @@ extern "C" int32_t ssw_default_tile_rows(int32_t heads, int32_t head_dim, int dt
 extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t head_dim, const ssw_plan_layout* L,
                               const int32_t* plan, const float* table, const int32_t rpb_window[3], float scale,
                               int use_mask, void* out, void* attn_vals, void* stream_) {
+  void* outs[1] = {out};
+  return ssw_attn_fused_multi(qkv, dtype, heads, head_dim, L, plan, table, rpb_window, scale, use_mask, outs, 1, attn_vals,
+                              stream_);
+}
+
+extern "C" int ssw_attn_fused_multi(const void* qkv, int dtype, int32_t heads, int32_t head_dim, const ssw_plan_layout* L,
+                                    const int32_t* plan, const float* table, const int32_t rpb_window[3], float scale,
+                                    int use_mask, void* const* outs, int32_t n_outs, void* attn_vals, void* stream_) {
   if (!L || !plan || !table || !rpb_window || heads <= 0 || head_dim <= 0) return SSW_E_INVALID;
+  if (!outs || n_outs < 1 || n_outs > kMaxOuts) return SSW_E_INVALID;
   if (L->n_vox == 0) return SSW_OK;
+  void* out = outs[0];
   if (!qkv || !out) return SSW_E_INVALID;
+  for (int d = 0; d < n_outs; ++d)
+    if (!outs[d] || (reinterpret_cast<uintptr_t>(outs[d]) & 15)) return SSW_E_INVALID;
   const int elt = dtype == SSW_F32 ? 4 : (dtype == SSW_BF16 || dtype == SSW_F16) ? 2 : 0;
   if (!elt) return SSW_E_INVALID;
   const int C = heads * head_dim;
@@ -844,6 +859,8 @@ extern "C" int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t
   AttnParams p = {};
   p.qkv = qkv;
   p.out = out;
+  p.outs.n = n_outs;
+  for (int d = 0; d < n_outs; ++d) p.outs.base[d] = outs[d];
   p.attn_vals = attn_vals;
   p.header = const_cast<int32_t*>(plan + L->off_header);
   p.pack_desc = reinterpret_cast<const int4*>(plan + L->off_pack_desc);

@@ -109,7 +109,7 @@ __device__ __forceinline__ float pair_mask(int x) {
 template <typename T, int HD, bool kTableSmem, bool kMask>
 __device__ __forceinline__ void tile_head(const unsigned char* rows, int row_stride, int data_bytes, const int* svox,
                                           const unsigned char* zero_row, int slot0, int h, int C, const float* table_base,
-                                          int tstride, float qscale, T* out, int lane) {
+                                          int tstride, float qscale, const OutSet& outs, int lane) {
   const int qr = lane >> 2, qt = lane & 3, mi = lane >> 3;
   const unsigned char* r_lo = rows + (size_t)(slot0 + qr) * row_stride;
   const unsigned char* r_hi = r_lo + 8 * (size_t)row_stride;
@@ -184,8 +184,8 @@ __device__ __forceinline__ void tile_head(const unsigned char* rows, int row_str
   }
   const float inv_lo = __frcp_rn(l_lo + 1e-8f), inv_hi = __frcp_rn(l_hi + 1e-8f);  // ops.cu:164
   const int v_lo = svox[slot0 + qr], v_hi = svox[slot0 + qr + 8];
-  T* o_lo = out + (int64_t)(v_lo < 0 ? 0 : v_lo) * C + h * HD + qt * 2;
-  T* o_hi = out + (int64_t)(v_hi < 0 ? 0 : v_hi) * C + h * HD + qt * 2;
+  const int64_t off_lo = (int64_t)(v_lo < 0 ? 0 : v_lo) * C + h * HD + qt * 2;
+  const int64_t off_hi = (int64_t)(v_hi < 0 ? 0 : v_hi) * C + h * HD + qt * 2;
 #pragma unroll
   for (int n = 0; n < HD / 16; ++n) {
     float oa[4] = {0.f, 0.f, 0.f, 0.f}, ob[4] = {0.f, 0.f, 0.f, 0.f};
@@ -195,13 +195,18 @@ __device__ __forceinline__ void tile_head(const unsigned char* rows, int row_str
       mma16816<T>(oa, pl, vf[n][0], vf[n][1]);
       mma16816<T>(ob, pl, vf[n][2], vf[n][3]);
     }
-    if (v_lo >= 0) {
-      *reinterpret_cast<uint32_t*>(o_lo + n * 16) = pack2<T>(oa[0] * inv_lo, oa[1] * inv_lo);
-      *reinterpret_cast<uint32_t*>(o_lo + n * 16 + 8) = pack2<T>(ob[0] * inv_lo, ob[1] * inv_lo);
-    }
-    if (v_hi >= 0) {
-      *reinterpret_cast<uint32_t*>(o_hi + n * 16) = pack2<T>(oa[2] * inv_hi, oa[3] * inv_hi);
-      *reinterpret_cast<uint32_t*>(o_hi + n * 16 + 8) = pack2<T>(ob[2] * inv_hi, ob[3] * inv_hi);
+    const uint32_t a_lo = pack2<T>(oa[0] * inv_lo, oa[1] * inv_lo), b_lo = pack2<T>(ob[0] * inv_lo, ob[1] * inv_lo);
+    const uint32_t a_hi = pack2<T>(oa[2] * inv_hi, oa[3] * inv_hi), b_hi = pack2<T>(ob[2] * inv_hi, ob[3] * inv_hi);
+    for (int d = 0; d < outs.n; ++d) {
+      T* out = reinterpret_cast<T*>(outs.base[d]);
+      if (v_lo >= 0) {
+        *reinterpret_cast<uint32_t*>(out + off_lo + n * 16) = a_lo;
+        *reinterpret_cast<uint32_t*>(out + off_lo + n * 16 + 8) = b_lo;
+      }
+      if (v_hi >= 0) {
+        *reinterpret_cast<uint32_t*>(out + off_hi + n * 16) = a_hi;
+        *reinterpret_cast<uint32_t*>(out + off_hi + n * 16 + 8) = b_hi;
+      }
     }
   }
 }
@@ -332,8 +337,8 @@ __device__ __forceinline__ void unit_key_block(MmaUnit<HD>& u, const unsigned ch
 // (each lane owns two adjacent channels per 8-channel block of rows lane/4 and lane/4 + 8).
 // `svox`: voxel of every slot, -1 for unused.
 template <typename T, int HD>
-__device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, const int* svox, int slot0, int h, int C, T* out,
-                                            int lane) {
+__device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, const int* svox, int slot0, int h, int C,
+                                            const OutSet& outs, int lane) {
   const int qr = lane >> 2, qt = lane & 3;
   // row sums live in four lanes each
   float ll = u.l_lo, lh = u.l_hi;
@@ -343,15 +348,18 @@ __device__ __forceinline__ void unit_finish(const MmaUnit<HD>& u, const int* svo
   lh += __shfl_xor_sync(0xffffffffu, lh, 2);
   const float inv_lo = __frcp_rn(ll + 1e-8f), inv_hi = __frcp_rn(lh + 1e-8f);  // ops.cu:164
   const int v_lo = svox[slot0 + qr], v_hi = svox[slot0 + qr + 8];
-  if (v_lo >= 0) {
-    T* o = out + (int64_t)v_lo * C + h * HD + qt * 2;
+  for (int d = 0; d < outs.n; ++d) {
+    T* out = reinterpret_cast<T*>(outs.base[d]);
+    if (v_lo >= 0) {
+      T* o = out + (int64_t)v_lo * C + h * HD + qt * 2;
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) *reinterpret_cast<uint32_t*>(o + n * 8) = pack2<T>(u.o[n][0] * inv_lo, u.o[n][1] * inv_lo);
-  }
-  if (v_hi >= 0) {
-    T* o = out + (int64_t)v_hi * C + h * HD + qt * 2;
+      for (int n = 0; n < HD / 8; ++n) *reinterpret_cast<uint32_t*>(o + n * 8) = pack2<T>(u.o[n][0] * inv_lo, u.o[n][1] * inv_lo);
+    }
+    if (v_hi >= 0) {
+      T* o = out + (int64_t)v_hi * C + h * HD + qt * 2;
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) *reinterpret_cast<uint32_t*>(o + n * 8) = pack2<T>(u.o[n][2] * inv_hi, u.o[n][3] * inv_hi);
+      for (int n = 0; n < HD / 8; ++n) *reinterpret_cast<uint32_t*>(o + n * 8) = pack2<T>(u.o[n][2] * inv_hi, u.o[n][3] * inv_hi);
+    }
   }
 }
 
@@ -527,7 +535,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMmaGroups + 32 * kMaxPr
         for (int un = cw; un < n_mt * H; un += n_cons_warps) {
           const int h = un / n_mt, mt = un - h * n_mt;
           tile_head<T, HD, kTableSmem, kMask>(rows, p.row_stride, data_bytes, svox, zero_row, mt * 16, h, C, table_base,
-                                              tstride, qscale, reinterpret_cast<T*>(p.out), lane);
+                                              tstride, qscale, p.outs, lane);
         }
       } else {
         const int nkb = cpad >> 4;  // 16-key blocks per window
@@ -540,7 +548,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMmaGroups + 32 * kMaxPr
             unit_key_block<T, HD, kTableSmem, kMask>(u, rows, p.row_stride, data_bytes, zero_row, kbase + kb * 16,
                                                      (C + h * HD) * (int)sizeof(T), (2 * C + h * HD) * (int)sizeof(T),
                                                      table_base, tstride, h, qscale, lane);
-          unit_finish<T, HD>(u, svox, mt * 16, h, C, reinterpret_cast<T*>(p.out), lane);
+          unit_finish<T, HD>(u, svox, mt * 16, h, C, p.outs, lane);
         }
       }
       __syncwarp();
@@ -690,7 +698,7 @@ __global__ void __launch_bounds__(kMmaGroupWarps * 32 * kMmaGroups + 32 * kMaxPr
         }
         if (active && !timed_out)
           unit_finish<T, HD>(u, reinterpret_cast<const int*>(q_stage + kMmaStageVoxOff), mt * 16, h, C,
-                             reinterpret_cast<T*>(p.out), lane);
+                             p.outs, lane);
       }
       __syncwarp();
       if (lane == 0 && !timed_out) mbar_arrive(qempty);

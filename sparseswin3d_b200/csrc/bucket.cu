@@ -27,6 +27,7 @@ struct KeySrc {
   int dims[3], dims_p[3], ws[3], ss[3], nwin[3];
   int n_per_window, n_windows;
   int rpbw[3];
+  int win_lo, win_hi;      // only voxels of windows [win_lo, win_hi) are bucketed
 };
 
 // (window, pos, region) of voxel v; false when the row is outside the grid / tables.
@@ -84,6 +85,7 @@ __global__ void k_count(KeySrc s, int64_t n, int words, int32_t* __restrict__ co
     atomicOr(reinterpret_cast<unsigned*>(header + SSW_H_ERROR), SSW_DEV_BAD_COORD);
     return;
   }
+  if (w < s.win_lo || w >= s.win_hi) return;  // another shard's window
   uint32_t bit = 1u << (pos & 31);
   uint32_t old = atomicOr(bitmap + (int64_t)w * words + (pos >> 5), bit);
   if (old & bit) {
@@ -342,7 +344,7 @@ __global__ void k_scatter(KeySrc s, int64_t n, int words, const int32_t* __restr
   int w = 0, pos = 0, r = 0;
   const bool ok = v < n && load_key(s, v, w, pos, r);  // coordinates are an input, not a product of the chain
   grid_dependency_wait();
-  if (!ok) return;
+  if (!ok || w < s.win_lo || w >= s.win_hi) return;
   int k = compact[w];
   if (k < 0) return;
   const uint32_t* bm = bitmap + (int64_t)w * words;
@@ -388,6 +390,8 @@ static void fill_keysrc(KeySrc& s, const int32_t* coords, const ssw_geometry* g,
   }
   s.n_windows = n_windows;
   s.n_per_window = n_per_window;
+  s.win_lo = 0;
+  s.win_hi = 0x7fffffff;
 }
 
 }  // namespace ssw
@@ -484,7 +488,16 @@ extern "C" int ssw_plan_layout_init(ssw_plan_layout* L, int64_t n_vox, int32_t n
 extern "C" int ssw_bucket_windows(const int32_t* coords, const ssw_geometry* geom, const int32_t* indices,
                                   const int8_t* mask, int32_t mask_windows, const int32_t rpb_window[3],
                                   const ssw_plan_layout* L, int32_t* plan, int32_t* scratch, void* stream_) {
+  return ssw_bucket_windows_range(coords, geom, indices, mask, mask_windows, rpb_window, L, plan, scratch, 0, 0x7fffffff,
+                                  stream_);
+}
+
+extern "C" int ssw_bucket_windows_range(const int32_t* coords, const ssw_geometry* geom, const int32_t* indices,
+                                        const int8_t* mask, int32_t mask_windows, const int32_t rpb_window[3],
+                                        const ssw_plan_layout* L, int32_t* plan, int32_t* scratch, int32_t win_lo,
+                                        int32_t win_hi, void* stream_) {
   if (!L || !plan || !scratch || !rpb_window) return SSW_E_INVALID;
+  if (win_lo < 0 || win_hi < win_lo) return SSW_E_INVALID;
   if ((coords != nullptr) == (indices != nullptr) && L->n_vox > 0) return SSW_E_INVALID;
   if (coords && !geom) return SSW_E_INVALID;
   if (coords && (geom->n_windows != L->n_windows || geom->n_per_window != L->n_per_window)) return SSW_E_INVALID;
@@ -509,6 +522,8 @@ extern "C" int ssw_bucket_windows(const int32_t* coords, const ssw_geometry* geo
   SSW_CUDA_TRY(cudaMemsetAsync(scratch, 0, sizeof(int32_t) * (size_t)L->off_partials, stream));
   KeySrc s;
   fill_keysrc(s, coords, geom, indices, mask, mask_windows, rpb_window, L->n_windows, n);
+  s.win_lo = win_lo;
+  s.win_hi = win_hi;
   int32_t* count = scratch + L->off_count;
   uint32_t* bitmap = reinterpret_cast<uint32_t*>(scratch + L->off_bitmap);
   int32_t* partials = scratch + L->off_partials;

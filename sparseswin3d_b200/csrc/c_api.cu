@@ -26,7 +26,25 @@ extern "C" const char* ssw_status_string(int status) {
 
 extern "C" const char* ssw_last_cuda_error(void) { return ssw::g_cuda_error; }
 
-extern "C" int ssw_version(void) { return 100; }
+extern "C" int ssw_version(void) { return 200; }
+
+extern "C" int ssw_enable_peer_access(int32_t peer_device) {
+  int dev = 0, can = 0;
+  SSW_CUDA_TRY(cudaGetDevice(&dev));
+  if (peer_device == dev) return SSW_OK;
+  SSW_CUDA_TRY(cudaDeviceCanAccessPeer(&can, dev, peer_device));
+  if (!can) return SSW_E_UNSUPPORTED;
+  const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();  // clear the sticky-free error state
+    return SSW_OK;
+  }
+  if (e != cudaSuccess) {
+    ssw::set_cuda_error(e, "cudaDeviceEnablePeerAccess");
+    return SSW_E_CUDA;
+  }
+  return SSW_OK;
+}
 
 // Host-side debug helper: the dependency edges of a captured CUDA graph as text, one edge per line,
 //   <from> -> <to> <full|programmatic> from_port=<p> to_port=<p>

@@ -2,17 +2,24 @@
 
 Windows never interact inside one attention call (the product is block diagonal by construction,
 sparse_swin/ops.cu:359-377) and scenes never interact (the batch index is folded into the window
-id, sparse_swin/swin3d_base.py:353), so the path shards without any exchange step:
+id, sparse_swin/swin3d_base.py:353), so the path shards without any exchange step on its inputs:
 
-* by scene: `scenes_of_rank` — rank r takes scenes r, r+world, ...;
-* by contiguous window range for one huge scene: `window_range_cuts` splits the non-empty windows
-  (in window-id order) into `world` contiguous ranges of equal estimated cost, `voxels_of_range`
-  selects the voxels of a range, every rank runs bucketing + fused attention on its own voxels, and
-  `gather_rows` (the only collective: an all-gather of finished output rows) rebuilds [N, C].
+* by scene: `scenes_of_rank` - rank r takes scenes r, r+world, ...;
+* by contiguous window range for one huge scene.  `plan_window_ranges` looks at the scene once (one
+  bucketing, one read-back) and cuts the dense window-id axis into `world` ranges of equal estimated
+  cost.  After that a pass needs no host synchronisation: every rank buckets the coordinates
+  restricted to its range (`bucket_windows(window_range=...)`: the N int32 keys are read by every
+  rank, only its own are sorted), runs the fused kernels on its windows, and the kernels store every
+  finished output row into the [N, C] buffer of EVERY rank (`PeerRows`: the same buffer mapped
+  across processes with CUDA IPC, plain stores over NVLink).  A barrier ends the pass; there is no
+  gather.  `gather_rows` is the collective alternative (an NCCL / gloo all-gather of finished rows)
+  for callers that cannot map peer memory.
 
-The collective goes through torch.distributed (NCCL on GPUs, gloo in the CPU tests)."""
+No TMA access to peer memory and no multicast is used: peer memory is only ever the target of
+ordinary stores issued by this library's own kernels."""
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 import torch
@@ -54,6 +61,58 @@ def voxels_of_range(perm: torch.Tensor, win_start: torch.Tensor, k0: int, k1: in
     return perm[a:b].to(torch.int64)
 
 
+def plan_window_ranges(coords: torch.Tensor, geom, world: int, alpha: float = 32.0, **plan_params) -> List[int]:
+    """Boundaries in DENSE window-id space, [b_0 = 0, b_1, ..., b_world = geom.n_windows]: rank r
+    works on the windows with ids in [b_r, b_{r+1}).  Looks at the scene once (one bucketing and one
+    read-back of the occupancies) - call it when the coordinates change, not per pass.  Every rank
+    computes the same boundaries from the same coordinates, so nothing is communicated."""
+    from . import window
+
+    full = window.bucket_windows(coords=coords, geom=geom, **plan_params)
+    counts = full.occupancy().cpu()
+    win_id = full.win_id[: counts.numel()].cpu()
+    cuts = window_range_cuts(counts, world, alpha)
+    bounds = [0]
+    for k in cuts[1:-1]:
+        bounds.append(int(win_id[k]) if k < win_id.numel() else int(geom.n_windows))
+    bounds.append(int(geom.n_windows))
+    return bounds
+
+
+class PeerRows:
+    """An [N, C] output buffer that exists on every rank and that the kernels of every rank can
+    store to: each rank allocates its own, the CUDA IPC handles go round once through the process
+    group (`all_gather_object`), every rank maps the others' buffers and enables peer access.
+    `ptrs` are the device addresses of the peers' buffers (own buffer excluded), ready for
+    `window_attention_fused(..., out=local, peer_out_ptrs=ptrs)`.  Only this library's kernels ever
+    touch the mapped peer tensors."""
+
+    def __init__(self, n: int, c: int, dtype: torch.dtype, device: torch.device, group=None):
+        import torch.distributed as dist
+        from torch.multiprocessing.reductions import reduce_tensor
+
+        from ._lib import check, lib
+
+        self.local = torch.zeros((n, c), dtype=dtype, device=device)
+        self.peers = []
+        self.ptrs = []
+        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+            return                      # a single process: the local buffer is all there is
+        world = dist.get_world_size(group)
+        rank = dist.get_rank(group)
+        torch.cuda.synchronize(device)
+        handles: list = [None] * world
+        dist.all_gather_object(handles, reduce_tensor(self.local), group=group)
+        for r, (rebuild, args) in enumerate(handles):
+            if r == rank:
+                continue
+            t = rebuild(*args)          # a tensor on the owner's device, backed by the owner's memory
+            check(lib.ssw_enable_peer_access(t.device.index), "ssw_enable_peer_access")
+            self.peers.append(t)
+            self.ptrs.append(t.data_ptr())
+        dist.barrier(group=group)       # nobody proceeds (or frees) before everyone has mapped
+
+
 def gather_rows(local_rows: torch.Tensor, local_ids: torch.Tensor, n_total: int, group=None) -> torch.Tensor:
     """All-gather finished output rows.  `local_rows` [n_r, C] are this rank's rows, `local_ids`
     [n_r] their voxel ids in the full scene.  Ranks hold different numbers of rows, so both are
@@ -82,36 +141,49 @@ def gather_rows(local_rows: torch.Tensor, local_ids: torch.Tensor, n_total: int,
     return out
 
 
+@dataclass
+class ShardedPass:
+    """What `sharded_window_attention` leaves behind: this rank's plan, the buffer that holds the
+    complete output once the closing collective has passed, and `error` - a one-element int32 device
+    tensor, non-zero when ANY rank's plan or kernels recorded an error bit (the closing collective
+    carries it, so no rank has to be asked)."""
+    plan: object
+    out: torch.Tensor
+    error: Optional[torch.Tensor] = None
+
+
 def sharded_window_attention(coords: torch.Tensor, qkv: torch.Tensor, geom, table: torch.Tensor, scale: float,
-                             rpb_window: Sequence[int], rank: int, world: int, group=None,
-                             alpha: float = 32.0, gather: bool = True):
+                             rpb_window: Sequence[int], rank: int, world: int, bounds: Sequence[int],
+                             rows: Optional[PeerRows] = None, group=None, scratch: Optional[torch.Tensor] = None,
+                             plan_buffer: Optional[torch.Tensor] = None) -> ShardedPass:
     """One attention pass over a single scene sharded by contiguous window ranges.
 
-    Every rank buckets the whole coordinate set (N int32 keys: cheap, replicated, and it keeps the
-    cut points identical everywhere without communication), takes its window range, runs the fused
-    kernel on its own voxels' qkv rows and, if `gather`, all-gathers the output rows.
-    Returns (out, ids): the full [N, C] output (or this rank's rows) and this rank's voxel ids."""
-    from . import attention, window
+    `bounds` come from `plan_window_ranges` (once per scene).  With `rows` (a `PeerRows`) the
+    kernels store each finished row on every rank, and the pass ends with a one-word all-reduce on
+    the stream (the maximum of the ranks' error words): it orders every rank's stores before
+    whatever the caller enqueues next and costs no host synchronisation; `rows.local` is then the
+    full [N, C] output.  A caller whose consumer of one pass may still run while the next pass
+    stores should alternate two `PeerRows`.  Without `rows` the finished rows are all-gathered with
+    `gather_rows` (which reads the row counts back: one host synchronisation)."""
+    from . import _lib, attention, window
 
     H, hd = qkv.shape[2], qkv.shape[3]
     pp = attention.plan_params(H, hd, qkv.dtype, rpb_window)
-    full = window.bucket_windows(coords=coords, geom=geom, **pp)
-    counts = full.occupancy()
-    cuts = window_range_cuts(counts, world, alpha)
-    ids = voxels_of_range(full.perm, full.win_start, cuts[rank], cuts[rank + 1])
-    if ids.numel():
-        sub_coords = coords.index_select(0, ids).contiguous()
-        sub_qkv = qkv.index_select(0, ids).contiguous()
-        plan = window.bucket_windows(coords=sub_coords, geom=geom, **pp)
-        local = attention.window_attention_fused(sub_qkv, plan, table, scale, use_mask=bool(geom.shifted))
-    else:
-        local = torch.empty((0, H * hd), dtype=qkv.dtype, device=qkv.device)
-    if not gather or world == 1:
-        return (local if world > 1 or not gather else _place(local, ids, coords.shape[0])), ids
-    return gather_rows(local, ids, coords.shape[0], group), ids
+    plan = window.bucket_windows(coords=coords, geom=geom, scratch=scratch, plan_buffer=plan_buffer,
+                                 window_range=(bounds[rank], bounds[rank + 1]), **pp)
+    if rows is not None:
+        attention.window_attention_fused(qkv, plan, table, scale, use_mask=bool(geom.shifted), out=rows.local,
+                                         peer_out_ptrs=rows.ptrs)
+        error = plan.header[_lib.H_ERROR:_lib.H_ERROR + 1].clone()
+        if world > 1:
+            import torch.distributed as dist
 
-
-def _place(rows: torch.Tensor, ids: torch.Tensor, n_total: int) -> torch.Tensor:
-    out = torch.empty((n_total, rows.shape[1]), dtype=rows.dtype, device=rows.device)
-    out.index_copy_(0, ids, rows)
-    return out
+            dist.all_reduce(error, op=dist.ReduceOp.MAX, group=group)
+        return ShardedPass(plan, rows.local, error)
+    out = torch.empty((coords.shape[0], H * hd), dtype=qkv.dtype, device=qkv.device)
+    attention.window_attention_fused(qkv, plan, table, scale, use_mask=bool(geom.shifted), out=out)
+    if world == 1:
+        return ShardedPass(plan, out, plan.header[_lib.H_ERROR:_lib.H_ERROR + 1].clone())
+    n_own = int(plan.header[_lib.H_N])
+    ids = plan.perm[:n_own].to(torch.int64)
+    return ShardedPass(plan, gather_rows(out.index_select(0, ids), ids, coords.shape[0], group))

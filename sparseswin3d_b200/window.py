@@ -127,7 +127,8 @@ def bucket_windows(*, coords: Optional[torch.Tensor] = None, geom: Optional[Geom
                    indices: Optional[torch.Tensor] = None, n_windows: Optional[int] = None,
                    n_per_window: Optional[int] = None, mask: Optional[torch.Tensor] = None,
                    rpb_window: Sequence[int] = (7, 7, 7), tile_rows: int = 64, padded: bool = False,
-                   scratch: Optional[torch.Tensor] = None, plan_buffer: Optional[torch.Tensor] = None) -> WindowPlan:
+                   scratch: Optional[torch.Tensor] = None, plan_buffer: Optional[torch.Tensor] = None,
+                   window_range: Optional[Sequence[int]] = None) -> WindowPlan:
     """Sort voxels by (window, pos) on the device and build the fused kernel's work list.
 
     Give either ``coords`` [N,4] + ``geom`` (pad, cyclic shift, partition and region ids are
@@ -138,7 +139,11 @@ def bucket_windows(*, coords: Optional[torch.Tensor] = None, geom: Optional[Geom
     ``tile_rows`` and ``padded`` shape the fused kernel's work list; take them from
     ``attention.plan_params(heads, head_dim, dtype, window)`` for the tensor the plan will serve.
     ``scratch`` and ``plan_buffer`` (int32 device tensors, reused when large enough) let a caller
-    that builds plans repeatedly keep the call free of allocations."""
+    that builds plans repeatedly keep the call free of allocations.
+
+    ``window_range`` = (lo, hi) buckets only the voxels whose window id lies in [lo, hi) - one GPU's
+    share of a scene that is split by contiguous window ranges (see ``shard``).  Voxel ids in the plan
+    still refer to the full arrays; ``inv_perm`` is defined for the voxels taken only."""
     if (coords is None) == (indices is None):
         raise _lib.SswError("give exactly one of coords= or indices=")
     if coords is not None:
@@ -170,7 +175,8 @@ def bucket_windows(*, coords: Optional[torch.Tensor] = None, geom: Optional[Geom
     if scratch is None or scratch.numel() < L.scratch_ints:
         scratch = torch.empty(max(L.scratch_ints, 1), dtype=torch.int32, device=dev)
     rw = (_lib.i32 * 3)(*[int(x) for x in rpb_window])
-    check(lib.ssw_bucket_windows(ptr(coords), geom, ptr(indices), ptr(mask), 0 if mask is None else mask.shape[0],
-                                 rw, L, ptr(plan), ptr(scratch), stream_ptr(dev)), "ssw_bucket_windows")
+    lo, hi = (0, 0x7FFFFFFF) if window_range is None else (int(window_range[0]), int(window_range[1]))
+    check(lib.ssw_bucket_windows_range(ptr(coords), geom, ptr(indices), ptr(mask), 0 if mask is None else mask.shape[0],
+                                       rw, L, ptr(plan), ptr(scratch), lo, hi, stream_ptr(dev)), "ssw_bucket_windows")
     has_regions = mask is not None or (coords is not None and bool(geom.shifted))
     return WindowPlan(L, plan, tuple(int(x) for x in rpb_window), has_regions)

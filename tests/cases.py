@@ -69,3 +69,19 @@ def room_crop_case(shift=(0, 0, 0), crop=200, heads=3, head_dim=32, window=(7, 7
     return dict(coords=coords, dims=dims, batch=1, window=window, shift=shift, indices=idx, n_windows=Bw, n=n, ws=ws,
                 ss=ss, dims_p=dp, qkv=qkv, table=table, rpi=O.relative_position_index(window), mask=mask, heads=heads,
                 head_dim=head_dim, scale=head_dim ** -0.5)
+
+
+def skewed_case(grid=27, shift=(4, 4, 4), heads=6, head_dim=32, seed=3):
+    """The skewed-occupancy stress shape at reduced size: window 9^3, half of the windows completely
+    full (729 voxels), the rest with 1-8 voxels."""
+    window = (9, 9, 9)
+    coords_np, dims = scenes.skewed_scene(grid=grid, window=9, p_dense=0.5, seed=seed)
+    coords = torch.from_numpy(coords_np)
+    idx, Bw, n, ws, ss, dp = O.window_keys(coords, 1, dims, window, shift)
+    g = torch.Generator().manual_seed(7 + seed)
+    qkv = torch.randn(coords.shape[0], 3, heads, head_dim, generator=g)
+    table = torch.randn(17 ** 3, heads, generator=g) * 0.5
+    mask = O.compute_mask(dp, ws, ss) if any(s > 0 for s in ss) else None
+    return dict(coords=coords, dims=dims, batch=1, window=window, shift=shift, indices=idx, n_windows=Bw, n=n, ws=ws,
+                ss=ss, dims_p=dp, qkv=qkv, table=table, rpi=O.relative_position_index(window), mask=mask, heads=heads,
+                head_dim=head_dim, scale=head_dim ** -0.5)

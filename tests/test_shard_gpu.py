@@ -1,4 +1,7 @@
-"""Window-range sharding on real GPUs (needs 2): the sharded pass equals the single-GPU pass."""
+"""Window-range sharding.  On one GPU: a scene bucketed range by range into one output buffer, and
+the multi-destination store, equal the single pass bit for bit.  On two GPUs (skipped when the box
+has one): ranks store their rows into each other's buffers and both end up with the single-GPU
+output, bit for bit; so does the all-gather alternative."""
 import os
 import socket
 
@@ -8,25 +11,77 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("world", [2, 5])
+def test_ranges_on_one_gpu_equal_single_pass(dtype, world):
+    from sparseswin3d_b200 import attention, shard, window
+    from tests.cases import make_case, skewed_case
+
+    dev = torch.device("cuda:0")
+    for case in (make_case(n_vox=6000, grid=48, shift=(3, 3, 3), seed=41), skewed_case()):
+        geom = window.resolve_geometry(case["batch"], case["dims"], case["window"], case["shift"])
+        coords, qkv, table = case["coords"].to(dev), case["qkv"].to(dtype).to(dev), case["table"].to(dev)
+        pp = attention.plan_params(case["heads"], case["head_dim"], dtype, case["window"])
+        use_mask = bool(geom.shifted)
+        full = window.bucket_windows(coords=coords, geom=geom, **pp)
+        ref = attention.window_attention_fused(qkv, full, table, case["scale"], use_mask=use_mask)
+        bounds = shard.plan_window_ranges(coords, geom, world, **pp)
+        assert bounds[0] == 0 and bounds[-1] == geom.n_windows and all(a <= b for a, b in zip(bounds, bounds[1:]))
+        out = torch.full_like(ref, float("nan"))
+        twin = torch.full_like(ref, float("nan"))          # stands for a peer's buffer
+        taken = 0
+        costs = []
+        for r in range(world):
+            plan = window.bucket_windows(coords=coords, geom=geom, window_range=(bounds[r], bounds[r + 1]), **pp)
+            attention.window_attention_fused(qkv, plan, table, case["scale"], use_mask=use_mask, out=out,
+                                             peer_out_ptrs=[twin.data_ptr()])
+            st = plan.stats()
+            assert st["error"] == 0
+            taken += st["voxels"]
+            costs.append(float(shard.window_cost(plan.occupancy().cpu()).sum()))
+        assert taken == coords.shape[0]
+        assert torch.equal(out, ref) and torch.equal(twin, ref)
+        # the estimate the cuts balance: no range above its share by more than the largest window
+        c_max = float(shard.window_cost(full.occupancy().cpu()).max())
+        assert max(costs) <= sum(costs) / world + c_max + 1e-6
+
+
 def _worker(rank, world, port, q):
     import torch.distributed as dist
 
     from sparseswin3d_b200 import attention, shard, window
     from tests.cases import make_case
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        case = make_case(n_vox=6000, grid=48, shift=(3, 3, 3), seed=41)
-        geom = window.resolve_geometry(1, case["dims"], case["window"], case["shift"])
-        coords, qkv, table = case["coords"].to(dev), case["qkv"].to(dev), case["table"].to(dev)
-        out, ids = shard.sharded_window_attention(coords, qkv, geom, table, case["scale"], case["window"], rank, world)
-        plan = window.bucket_windows(coords=coords, geom=geom, **attention.plan_params(3, 32, torch.float32, case["window"]))
-        ref = attention.window_attention_fused(qkv, plan, table, case["scale"], use_mask=True)
-        torch.cuda.synchronize()
-        q.put((rank, bool(torch.equal(out, ref)), int(ids.numel())))
+        ok = []
+        for dtype in (torch.float32, torch.bfloat16):
+            case = make_case(n_vox=6000, grid=48, shift=(3, 3, 3), seed=41)
+            geom = window.resolve_geometry(1, case["dims"], case["window"], case["shift"])
+            coords, qkv, table = case["coords"].to(dev), case["qkv"].to(dtype).to(dev), case["table"].to(dev)
+            pp = attention.plan_params(3, 32, dtype, case["window"])
+            ref = attention.window_attention_fused(qkv, window.bucket_windows(coords=coords, geom=geom, **pp), table,
+                                                   case["scale"], use_mask=True)
+            bounds = shard.plan_window_ranges(coords, geom, world, **pp)
+            rows = shard.PeerRows(coords.shape[0], 96, dtype, dev)
+            rows.local.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            for _ in range(2):   # a second pass over the same buffers
+                res = shard.sharded_window_attention(coords, qkv, geom, table, case["scale"], case["window"], rank, world,
+                                                     bounds, rows=rows)
+            torch.cuda.synchronize()
+            n_own = res.plan.stats()["voxels"]
+            ok.append(bool(torch.equal(res.out, ref)) and res.plan.stats()["error"] == 0 and 1000 < n_own < 5000)
+            gathered = shard.sharded_window_attention(coords, qkv, geom, table, case["scale"], case["window"], rank, world,
+                                                      bounds)
+            ok.append(bool(torch.equal(gathered.out, ref)))
+            dist.barrier()
+            del rows
+        q.put((rank, ok))
     finally:
         dist.destroy_process_group()
 
@@ -47,5 +102,4 @@ def test_sharded_pass_equals_single_gpu():
         p.join(300)
         assert p.exitcode == 0
     res = [q.get(timeout=10) for _ in range(2)]
-    assert all(ok for _, ok, _ in res)
-    assert sum(n for _, _, n in res) == 6000 and min(n for _, _, n in res) > 1000
+    assert all(all(ok) for _, ok in res), res
