@@ -634,7 +634,7 @@ def skewed_shard(dev, rank, world, steps=10, warm=3, grid=126, dtype=torch.bfloa
            "bitwise_equal_to_single_gpu_pass_on_every_rank": same_all, "error_word": err,
            "host_synchronisations_per_pass": 0, "collectives_per_pass": "one 4-byte all-reduce (max of the error words)"}
     barrier()
-    del rows
+    rows.close()
     return out
 
 

@@ -207,8 +207,9 @@ int ssw_attn_fused(const void* qkv, int dtype, int32_t heads, int32_t head_dim,
 
 /* ssw_attn_fused with several destination buffers: every finished output row is stored to
  * outs[0..n_outs-1] (1 <= n_outs <= 8), each an [N, heads*head_dim] buffer of `dtype`.  outs[0] is
- * the caller's own; the others are the same buffer on peer GPUs of the node, mapped into this
- * process (CUDA IPC) with peer access enabled: this is how one scene split over several GPUs by
+ * the caller's own; the others are the same buffer on peer GPUs of the node, mapped into the
+ * context of the launching device (ssw_peer_buffer_open for another process's buffer,
+ * ssw_enable_peer_access for another device of this process): this is how one scene split over several GPUs by
  * window ranges ends with the complete output on every GPU and no gather step - plain stores over
  * NVLink from the kernel's epilogue.  Upstream has no multi-GPU path (it relies on its trainer's
  * data parallelism); the single-destination semantics are those of ssw_attn_fused. */
@@ -219,6 +220,18 @@ int ssw_attn_fused_multi(const void* qkv, int dtype, int32_t heads, int32_t head
 /* Host only: lets kernels on the current device store to memory of `peer_device` (cudaDeviceEnablePeerAccess;
  * "already enabled" is not an error).  SSW_E_UNSUPPORTED when the two devices cannot reach each other. */
 int ssw_enable_peer_access(int32_t peer_device);
+/* Host only: an output buffer that kernels of OTHER PROCESSES on the node can store to.
+ * _create allocates `bytes` of zeroed device memory on the current device (cudaMalloc: this call
+ * allocates, it belongs to set-up, not to a pass) and writes its CUDA IPC handle (SSW_IPC_HANDLE_BYTES
+ * bytes, to be sent to the peers by any host channel).  _open maps a peer's buffer into the context of
+ * the CURRENT device - the device whose kernels will store to it; a mapping made under another device
+ * of this process is not reachable from the launching device and faults - and enables peer access as
+ * needed.  _close unmaps an opened buffer; every peer must have closed before the owner calls _destroy. */
+#define SSW_IPC_HANDLE_BYTES 64
+int ssw_peer_buffer_create(int64_t bytes, void** ptr, unsigned char* handle);
+int ssw_peer_buffer_open(const unsigned char* handle, void** ptr);
+int ssw_peer_buffer_close(void* ptr);
+int ssw_peer_buffer_destroy(void* ptr);
 
 /* Backward of ssw_attn_fused: gradients of qkv and of the bias table from the gradient of `out`,
  * with the probabilities recomputed instead of stored.  It replaces what upstream's autograd runs

@@ -63,6 +63,10 @@ def _load() -> C.CDLL:
         "ssw_attn_fused": (C.c_int, [vp, C.c_int, i32, i32, P(PlanLayout), vp, vp, P(i32), f32, C.c_int, vp, vp, vp]),
         "ssw_attn_fused_multi": (C.c_int, [vp, C.c_int, i32, i32, P(PlanLayout), vp, vp, P(i32), f32, C.c_int, P(vp), i32, vp, vp]),
         "ssw_enable_peer_access": (C.c_int, [i32]),
+        "ssw_peer_buffer_create": (C.c_int, [i64, P(vp), C.c_char_p]),
+        "ssw_peer_buffer_open": (C.c_int, [C.c_char_p, P(vp)]),
+        "ssw_peer_buffer_close": (C.c_int, [vp]),
+        "ssw_peer_buffer_destroy": (C.c_int, [vp]),
         "ssw_bucket_windows_range": (C.c_int, [vp, P(Geometry), vp, vp, i32, P(i32), P(PlanLayout), vp, vp, i32, i32, vp]),
         "ssw_attn_fused_bwd_workspace_floats": (i64, [i64, i32]),
         "ssw_attn_fused_bwd": (C.c_int, [vp, vp, C.c_int, i32, i32, P(PlanLayout), vp, vp, P(i32), f32, C.c_int, vp, vp, vp, vp]),

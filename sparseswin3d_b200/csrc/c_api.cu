@@ -46,6 +46,47 @@ extern "C" int ssw_enable_peer_access(int32_t peer_device) {
   return SSW_OK;
 }
 
+static_assert(sizeof(cudaIpcMemHandle_t) == SSW_IPC_HANDLE_BYTES, "IPC handle size");
+
+extern "C" int ssw_peer_buffer_create(int64_t bytes, void** ptr, unsigned char* handle) {
+  if (bytes <= 0 || !ptr || !handle) return SSW_E_INVALID;
+  void* p = nullptr;
+  SSW_CUDA_TRY(cudaMalloc(&p, (size_t)bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaMemset(p, 0, (size_t)bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    (void)cudaFree(p);
+    ssw::set_cuda_error(e, "ssw_peer_buffer_create");
+    return SSW_E_CUDA;
+  }
+  memcpy(handle, &h, sizeof(h));
+  *ptr = p;
+  return SSW_OK;
+}
+
+extern "C" int ssw_peer_buffer_open(const unsigned char* handle, void** ptr) {
+  if (!handle || !ptr) return SSW_E_INVALID;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  // opened in the context of the current device: that is the device whose kernels will use *ptr
+  SSW_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return SSW_OK;
+}
+
+extern "C" int ssw_peer_buffer_close(void* ptr) {
+  if (!ptr) return SSW_E_INVALID;
+  SSW_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return SSW_OK;
+}
+
+extern "C" int ssw_peer_buffer_destroy(void* ptr) {
+  if (!ptr) return SSW_E_INVALID;
+  SSW_CUDA_TRY(cudaFree(ptr));
+  return SSW_OK;
+}
+
 // Host-side debug helper: the dependency edges of a captured CUDA graph as text, one edge per line,
 //   <from> -> <to> <full|programmatic> from_port=<p> to_port=<p>
 // with nodes written as <index>:<name>, kernel nodes named by their function and other nodes by

@@ -79,38 +79,76 @@ def plan_window_ranges(coords: torch.Tensor, geom, world: int, alpha: float = 32
     return bounds
 
 
+class _DeviceBytes:
+    """Lets torch view raw device memory (no copy, no ownership) through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
 class PeerRows:
     """An [N, C] output buffer that exists on every rank and that the kernels of every rank can
-    store to: each rank allocates its own, the CUDA IPC handles go round once through the process
-    group (`all_gather_object`), every rank maps the others' buffers and enables peer access.
-    `ptrs` are the device addresses of the peers' buffers (own buffer excluded), ready for
-    `window_attention_fused(..., out=local, peer_out_ptrs=ptrs)`.  Only this library's kernels ever
-    touch the mapped peer tensors."""
+    store to.  Each rank allocates its own (`ssw_peer_buffer_create`), the CUDA IPC handles go round
+    once through the process group, and every rank maps the others' buffers into the context of ITS
+    OWN device (`ssw_peer_buffer_open`) - the device whose kernels will store to them.  (A mapping
+    made under the owner's device index, as `torch.multiprocessing`'s tensor rebuilding does, is
+    not reachable from kernels of this rank's device: they fault.)  `local` is this rank's buffer as
+    a tensor; `ptrs` are the device addresses of the peers' buffers, for
+    `window_attention_fused(..., out=local, peer_out_ptrs=ptrs)`.  Peer memory is only ever the
+    target of plain stores from this library's kernels; nothing else is given these addresses.
+
+    Call `close()` on every rank (it is collective) before the process group goes away."""
 
     def __init__(self, n: int, c: int, dtype: torch.dtype, device: torch.device, group=None):
+        import ctypes
+
         import torch.distributed as dist
-        from torch.multiprocessing.reductions import reduce_tensor
 
         from ._lib import check, lib
 
-        self.local = torch.zeros((n, c), dtype=dtype, device=device)
-        self.peers = []
-        self.ptrs = []
-        if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
-            return                      # a single process: the local buffer is all there is
-        world = dist.get_world_size(group)
-        rank = dist.get_rank(group)
-        torch.cuda.synchronize(device)
-        handles: list = [None] * world
-        dist.all_gather_object(handles, reduce_tensor(self.local), group=group)
-        for r, (rebuild, args) in enumerate(handles):
-            if r == rank:
-                continue
-            t = rebuild(*args)          # a tensor on the owner's device, backed by the owner's memory
-            check(lib.ssw_enable_peer_access(t.device.index), "ssw_enable_peer_access")
-            self.peers.append(t)
-            self.ptrs.append(t.data_ptr())
-        dist.barrier(group=group)       # nobody proceeds (or frees) before everyone has mapped
+        self.group = group
+        self.ptrs: List[int] = []
+        self._own = ctypes.c_void_p()
+        self._multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        nbytes = max(n * c * torch.empty((), dtype=dtype).element_size(), 16)
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(device):
+            check(lib.ssw_peer_buffer_create(nbytes, ctypes.byref(self._own), handle), "ssw_peer_buffer_create")
+            self.local = torch.as_tensor(_DeviceBytes(self._own.value, nbytes), device=device)[: n * c *
+                                         torch.empty((), dtype=dtype).element_size()].view(dtype).view(n, c)
+            if not self._multi:
+                return
+            world, rank = dist.get_world_size(group), dist.get_rank(group)
+            handles: list = [None] * world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            for r, h in enumerate(handles):
+                if r == rank:
+                    continue
+                p = ctypes.c_void_p()
+                check(lib.ssw_peer_buffer_open(h, ctypes.byref(p)), "ssw_peer_buffer_open")
+                self.ptrs.append(p.value)
+        dist.barrier(group=group)       # nobody stores before everyone has mapped
+
+    def close(self):
+        """Collective: every rank unmaps its peers' buffers, then every rank frees its own."""
+        from ._lib import check, lib
+
+        if self._own.value is None:
+            return
+        torch.cuda.synchronize(self.local.device)
+        with torch.cuda.device(self.local.device):
+            if self._multi:
+                import torch.distributed as dist
+
+                dist.barrier(group=self.group)      # no kernel of any rank still stores
+                for p in self.ptrs:
+                    check(lib.ssw_peer_buffer_close(p), "ssw_peer_buffer_close")
+                self.ptrs = []
+                dist.barrier(group=self.group)      # every mapping is gone before an owner frees
+            check(lib.ssw_peer_buffer_destroy(self._own), "ssw_peer_buffer_destroy")
+        self._own.value = None
+        self.local = None
 
 
 def gather_rows(local_rows: torch.Tensor, local_ids: torch.Tensor, n_total: int, group=None) -> torch.Tensor:

@@ -79,8 +79,7 @@ def _worker(rank, world, port, q):
             gathered = shard.sharded_window_attention(coords, qkv, geom, table, case["scale"], case["window"], rank, world,
                                                       bounds)
             ok.append(bool(torch.equal(gathered.out, ref)))
-            dist.barrier()
-            del rows
+            rows.close()
         q.put((rank, ok))
     finally:
         dist.destroy_process_group()
@@ -103,3 +102,28 @@ def test_sharded_pass_equals_single_gpu():
         assert p.exitcode == 0
     res = [q.get(timeout=10) for _ in range(2)]
     assert all(all(ok) for _, ok in res), res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_one_process_two_devices_peer_store():
+    """One process driving two devices: the second destination is an ordinary tensor on the other
+    device, reachable after `ssw_enable_peer_access`."""
+    from sparseswin3d_b200 import attention, window
+    from sparseswin3d_b200._lib import check, lib
+    from tests.cases import make_case
+
+    dev, other = torch.device("cuda:0"), torch.device("cuda:1")
+    case = make_case(n_vox=3000, grid=40, shift=(3, 3, 3), seed=8)
+    geom = window.resolve_geometry(1, case["dims"], case["window"], case["shift"])
+    with torch.cuda.device(dev):
+        check(lib.ssw_enable_peer_access(1), "ssw_enable_peer_access")
+        for dtype in (torch.float32, torch.bfloat16):
+            qkv = case["qkv"].to(dtype).to(dev)
+            plan = window.bucket_windows(coords=case["coords"].to(dev), geom=geom, **attention.plan_params(3, 32, dtype))
+            twin = torch.zeros(3000, 96, dtype=dtype, device=other)
+            torch.cuda.synchronize(other)
+            out = attention.window_attention_fused(qkv, plan, case["table"].to(dev), case["scale"], use_mask=True,
+                                                   peer_out_ptrs=[twin.data_ptr()])
+            torch.cuda.synchronize(dev)
+            assert plan.stats()["error"] == 0
+            assert torch.equal(twin.cpu(), out.cpu())
