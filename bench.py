@@ -532,6 +532,11 @@ def run_ours(args):
     res["secondary"] = secondary
     if not args.no_secondary:
         res["shard"] = shard_lines(dev, rank, world)
+        if rank == 0:
+            try:
+                res["stage"] = stage_line(dev, args.dtype, depth=6, reps=3)
+            except Exception as e:
+                res["stage"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
     if world > 1:
         dist.barrier()
     if rank == 0:
@@ -686,6 +691,69 @@ def run_skewed(args):
         dist.destroy_process_group()
 
 
+def stage_line(dev, dtype_name="f32", depth=6, reps=5):
+    """A whole Swin stage on the benchmark room (150 000 voxels, C=96, 3 heads x 32, window 7^3):
+    `depth` blocks alternating W-MSA and SW-MSA, each norm1 - qkv - attention core - proj - residual -
+    norm2 - MLP - residual (the four Linears are library GEMMs).  Three forms of the same forward,
+    each captured into a CUDA graph and replayed: the stage as built here (two plans per stage,
+    one-pass add + LayerNorm), plans still shared but the shell as separate torch operations, and
+    upstream's structure (every block buckets for itself, separate shell)."""
+    from sparseswin3d_b200 import scenes, stage
+
+    dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[dtype_name]
+    coords_np, dims = scenes.room_scene(N_VOX, seed=0)
+    coords = torch.from_numpy(coords_np).to(dev)
+    torch.manual_seed(0)
+    layer = stage.BasicLayer(dim=C, depth=depth, num_heads=HEADS, window_size=WINDOW, qkv_bias=True).to(dev).to(dtype).eval()
+    layer.strict = False
+    g = torch.Generator(device=dev).manual_seed(3)
+    feats = torch.randn(N_VOX, C, device=dev, generator=g).to(dtype)
+    x = stage.SparseVoxels(feats, coords, dims, 1)
+    out = {}
+    ref = None
+    for name, reuse, fuse in (("stage", True, True), ("shared_plans_torch_shell", True, False),
+                              ("per_block_bucketing_torch_shell", False, False)):
+        layer.reuse_plans, layer.fuse_shell = reuse, fuse
+        with torch.no_grad():
+            for _ in range(3):
+                y = layer(x).features
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream(device=dev)
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(gr, stream=side):
+                    y = layer(x).features
+        for _ in range(3):
+            gr.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(4):
+                gr.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) / 4)
+        ms = statistics.median(ts)
+        if ref is None:
+            ref = y.float().clone()
+        dev_rel = float(((y.float() - ref).abs().max() / ref.abs().max()).item())
+        out[name] = {"ms_per_forward": ms, "voxel_blocks_per_s": N_VOX * depth / (ms * 1e-3), "max_rel_dev_from_stage": dev_rel}
+        del gr
+    return {"workload": f"one Swin stage, depth {depth}, on the {N_VOX}-voxel room, C={C}, {HEADS} heads x {HEAD_DIM}, window 7^3, "
+                        f"{dtype_name}; bucketing from raw coordinates inside every forward",
+            "unit": "voxel-blocks/s", **out}
+
+
+def run_stage(args):
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    res = {"metric": "voxel-blocks/sec through one Swin stage", "n_gpus": 1, "data": "synthetic",
+           "lines": [stage_line(dev, dt, depth) for dt in ("f32", "bf16") for depth in (2, 6)]}
+    print(json.dumps(res), flush=True)
+
+
 # ------------------------------------------------------------------------------------------------
 # CPU legs: the oracle (a PyTorch CPU restatement of upstream; upstream itself has no CPU path)
 # ------------------------------------------------------------------------------------------------
@@ -816,7 +884,7 @@ def main():
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (other dtype, "
                                                                "same-scene control, window-range shard lines)")
-    ap.add_argument("--workload", default="room", choices=["room", "skewed"],
+    ap.add_argument("--workload", default="room", choices=["room", "skewed", "stage"],
                     help="room: the default line (W-MSA + SW-MSA on a 150k-voxel room); skewed: one 10^6-voxel "
                          "skewed-occupancy scene sharded by window ranges (secondary)")
     ap.add_argument("--blocks", type=int, default=0,
@@ -828,6 +896,8 @@ def main():
         run_reference(args)
     elif args.workload == "skewed":
         run_skewed(args)
+    elif args.workload == "stage":
+        run_stage(args)
     else:
         run_ours(args)
 

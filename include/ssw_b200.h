@@ -233,6 +233,18 @@ int ssw_peer_buffer_open(const unsigned char* handle, void** ptr);
 int ssw_peer_buffer_close(void* ptr);
 int ssw_peer_buffer_destroy(void* ptr);
 
+/* The element-wise shell of a Swin block between its GEMMs (swin3d_base.py:741-782: norm1, the
+ * residual add after attention, norm2, the residual add after the MLP) in one pass over the voxel
+ * rows: sum = a + b (b may be NULL: sum = a), norm = LayerNorm(sum) * gamma + beta over the
+ * `channels` of each row (biased variance, eps inside the square root, as torch.nn.LayerNorm).
+ * a, b, sum_out, norm_out: [n_rows, channels] of `dtype`, 16-byte aligned, channels * element size a
+ * multiple of 16 and at most 2048 bytes; sum_out may be a (in place) or NULL, norm_out may be NULL;
+ * gamma, beta: fp32 [channels].  With 16-bit rows the normalised value is the rounded sum, i.e. what
+ * a separate add followed by LayerNorm computes.  Statistics in fp32. */
+int ssw_add_layernorm(const void* a, const void* b, const float* gamma, const float* beta, float eps,
+                      int dtype, int64_t n_rows, int32_t channels, void* sum_out, void* norm_out,
+                      void* stream);
+
 /* Backward of ssw_attn_fused: gradients of qkv and of the bias table from the gradient of `out`,
  * with the probabilities recomputed instead of stored.  It replaces what upstream's autograd runs
  * for the same span: softmax_last_dim_backward (ops.cu:169-194, swin3d_base.py:177-188) and the

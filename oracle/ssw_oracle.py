@@ -494,3 +494,41 @@ def dense_window_attention(qkv, indices, scale, table, rpi, mask=None, acc_dtype
         pr = e / (e.sum(-1, keepdim=True) + 1e-8)
         out[vox] = (pr @ v).permute(1, 0, 2).reshape(len(p), H * hd)
     return out
+
+
+# --------------------------------------------------------------------------------------------------
+# One Swin block / one stage (sparse_swin/swin3d_base.py:741-782, 857-873), on plain CPU tensors
+# --------------------------------------------------------------------------------------------------
+def swin_block(feats, coords, batch, dims, window_size, shift_size, prm, num_heads, eps=1e-5, acc_dtype=torch.float64):
+    """SwinTransformerBlock.forward (swin3d_base.py:777-782): x + attn(norm1(x)) (forward_part1,
+    :741-769: pad, roll by -shift, partition, WindowAttentionSparse, reverse, roll back - the window
+    keys of `window_keys` are that chain's indices and the output order is the input's), then
+    x + mlp(norm2(x)) (forward_part2, :771-775; MLP :1144-1149 with exact GELU).  `prm` maps
+    upstream's parameter names inside the block (norm1.weight, attn.qkv.weight, ...) to tensors.
+    Dropout and stochastic depth are the identity (evaluation mode)."""
+    F = torch.nn.functional
+    x = feats.to(acc_dtype)
+    g = lambda k: prm[k].to(acc_dtype) if k in prm and prm[k] is not None else None
+    C = x.shape[1]
+    hd = C // num_heads
+    idx, _, n, ws, ss, dp = window_keys(coords, batch, dims, window_size, shift_size)
+    mask = compute_mask(dp, ws, ss) if any(s > 0 for s in ss) else None   # :755-760: mask only when shifted
+    h = F.layer_norm(x, (C,), g("norm1.weight"), g("norm1.bias"), eps)
+    qkv = F.linear(h, g("attn.qkv.weight"), g("attn.qkv.bias")).reshape(-1, 3, num_heads, hd)
+    core = dense_window_attention(qkv, idx, hd ** -0.5, g("attn.relative_position_bias_table"),
+                                  relative_position_index(window_size), mask, acc_dtype=acc_dtype)
+    x = x + F.linear(core, g("attn.proj.weight"), g("attn.proj.bias"))
+    h = F.layer_norm(x, (C,), g("norm2.weight"), g("norm2.bias"), eps)
+    m = F.linear(F.gelu(F.linear(h, g("mlp.linear1.weight"), g("mlp.linear1.bias"))), g("mlp.linear2.weight"),
+                 g("mlp.linear2.bias"))
+    return x + m
+
+
+def basic_layer(feats, coords, batch, dims, window_size, block_params, num_heads, eps=1e-5, acc_dtype=torch.float64):
+    """BasicLayer.forward without downsampling (swin3d_base.py:857-873): blocks alternate shift 0
+    and shift window // 2 (:835-836, :846)."""
+    shift = tuple(w // 2 for w in window_size)
+    x = feats
+    for i, prm in enumerate(block_params):
+        x = swin_block(x, coords, batch, dims, window_size, (0, 0, 0) if i % 2 == 0 else shift, prm, num_heads, eps, acc_dtype)
+    return x

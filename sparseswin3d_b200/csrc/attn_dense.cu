@@ -198,6 +198,15 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = p.H, C = p.C;
 
+  // Whether there is any window beyond a pack is a device-side count: a launch that finds none
+  // (the usual case on surface-sparse scenes) leaves before it sets anything up.
+  grid_dependency_wait();
+  {
+    BinTables bins0(const_cast<int32_t*>(p.bins), p.n_per_window);
+    const int W0 = min(max(p.header[SSW_H_W], 0), p.w_cap);
+    const int first = p.tile + 1 <= p.n_per_window + 1 ? min(max(bins0.wstart[p.tile + 1], 0), W0) : W0;
+    if (first >= W0) return;
+  }
   if (threadIdx.x == 0) {
     for (int j = 0; j < kDMaxKT; ++j) {
       mbar_init(kv_full + j, kDProd);
@@ -223,7 +232,6 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  grid_dependency_wait();
 
   // the windows beyond a pack, heaviest first: window slots [ws0, W) of the plan's pack order
   BinTables bins(const_cast<int32_t*>(p.bins), p.n_per_window);

@@ -549,9 +549,10 @@ __global__ void __maxnreg__(regs_for_threads(MAXT)) k_attn_fused(AttnParams p) {
             else
               attend_keys_split<HH, kTableSmem, false>(hs, rows, p.row_stride, data_bytes, kbeg, c,
                                                        (C + h * HD + x * HH) * 4, C, table_h, 0, lanes);
-            for (int d = 0; d < p.outs.n; ++d)
-              store_out<T, HH>(reinterpret_cast<T*>(p.outs.base[d]) + (int64_t)my_vox * C + h * HD + x * HH, hs,
-                               1.0f / (hs.l + 1e-8f));
+            const float inv_l = 1.0f / (hs.l + 1e-8f);  // ops.cu:164
+            store_out<T, HH>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD + x * HH, hs, inv_l);
+            for (int d = 1; d < p.outs.n; ++d)  // the same row on peer GPUs
+              store_out<T, HH>(reinterpret_cast<T*>(p.outs.base[d]) + (int64_t)my_vox * C + h * HD + x * HH, hs, inv_l);
           }
         }
         __syncwarp();
@@ -584,7 +585,8 @@ __global__ void __maxnreg__(regs_for_threads(MAXT)) k_attn_fused(AttnParams p) {
           }
           // Straight to global memory: each thread owns a 16-byte-aligned run of HD outputs of one
           // row (bulk stores of whole rows were tried; one bulk operation per row is what bounds them).
-          for (int d = 0; d < p.outs.n; ++d)
+          store_out<T, HD>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD, st, inv_l);
+          for (int d = 1; d < p.outs.n; ++d)  // the same row on peer GPUs
             store_out<T, HD>(reinterpret_cast<T*>(p.outs.base[d]) + (int64_t)my_vox * C + h * HD, st, inv_l);
         }
       }
@@ -712,9 +714,11 @@ __global__ void __maxnreg__(regs_for_threads(MAXT)) k_attn_fused(AttnParams p) {
         if constexpr (kHalf) fence_async_smem();  // the widened rows were written through the generic proxy
         __syncthreads();  // everyone done with this tile before it is overwritten
       }
-      if (row_active)
-        for (int d = 0; d < p.outs.n; ++d)
+      if (row_active) {
+        store_out<T, HB>(reinterpret_cast<T*>(p.out) + (int64_t)my_vox * C + h * HD + xh * HB, st, inv_l);
+        for (int d = 1; d < p.outs.n; ++d)  // the same row on peer GPUs
           store_out<T, HB>(reinterpret_cast<T*>(p.outs.base[d]) + (int64_t)my_vox * C + h * HD + xh * HB, st, inv_l);
+      }
     }
   }
 }

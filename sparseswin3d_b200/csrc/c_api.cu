@@ -107,6 +107,9 @@ static void node_name(cudaGraphNode_t n, char* out, size_t cap) {
       snprintf(out, cap, "%s", name);
       return;
     }
+    // a kernel the runtime cannot describe (a library's, loaded through the driver API): the failed
+    // query must not stay behind as the thread's last error
+    (void)cudaGetLastError();
     snprintf(out, cap, "kernel");
     return;
   }
@@ -157,6 +160,7 @@ extern "C" int ssw_debug_graph_edges(void* graph_, char* text, int64_t text_byte
   delete[] from;
   delete[] to;
   delete[] ed;
+  (void)cudaGetLastError();  // a read-only helper leaves no error state behind
   if (n_nodes) *n_nodes = (int64_t)nn;
   if (n_edges) *n_edges = (int64_t)ne;
   if (n_programmatic) *n_programmatic = prog;

@@ -38,8 +38,11 @@ def _load_upstream():
 
     sp = types.ModuleType("spconv.pytorch")
     sp.SparseModule, sp.SparseSequential = nn.Module, nn.Sequential
-    for name in ("SparseConvTensor", "SubMConv3d", "SparseConv3d", "SparseInverseConv3d"):
+    for name in ("SubMConv3d", "SparseConv3d", "SparseInverseConv3d"):
         setattr(sp, name, type(name, (), {}))
+    from sparseswin3d_b200.stage import SparseVoxels
+
+    sp.SparseConvTensor = SparseVoxels      # the container upstream's blocks assert on (swin3d_base.py:338)
     spconv = types.ModuleType("spconv")
     spconv.pytorch = sp
     builder = types.ModuleType("pointcept.models.builder")
@@ -136,3 +139,34 @@ def test_upstream_module_and_this_module_agree_forward_and_backward():
     yb, fb, tb, wb = run(theirs)
     assert rel_err(ya, yb) <= 1e-5
     assert rel_err(fa, fb) <= 1e-4 and rel_err(ta, tb) <= 1e-4 and rel_err(wa, wb) <= 1e-4
+
+
+@pytest.mark.parametrize("depth", [2, 3])
+def test_upstream_stage_and_this_stage_agree(depth):
+    """Upstream's own BasicLayer / SwinTransformerBlock (swin3d_base.py:680-873: pad, roll, partition,
+    attention, reverse, roll back, crop in every block, on this library's operators) against this
+    package's stage (two plans per stage, one-pass add + LayerNorm shell) with the same weights."""
+    from sparseswin3d_b200 import stage
+    from tests.cases import make_case
+
+    up = _load_upstream()
+    dev = torch.device("cuda:0")
+    dims, win = (20, 24, 22), (7, 7, 7)
+    case = make_case(n_vox=1200, dims=dims, window=win, seed=31)
+    C, H = 96, 3
+    torch.manual_seed(7)
+    ours = stage.BasicLayer(dim=C, depth=depth, num_heads=H, window_size=win, drop_path=[0.0] * depth, qkv_bias=True).to(dev)
+    with torch.no_grad():
+        for b in ours.blocks:
+            b.attn.relative_position_bias_table.normal_(0, 0.5)
+            b.norm1.weight.normal_(1, 0.2), b.norm1.bias.normal_(0, 0.2)
+    theirs = up.BasicLayer(dim=C, depth=depth, num_heads=H, window_size=win, drop_path=[0.0] * depth, qkv_bias=True).to(dev)
+    theirs.load_state_dict(ours.state_dict())                        # same parameter names, strict
+    ours.eval(), theirs.eval()
+    feats = torch.randn(1200, C, device=dev)
+    coords = case["coords"].to(dev)
+    with torch.no_grad():
+        ya = ours(stage.SparseVoxels(feats, coords, dims, 1)).features
+        yb_x = theirs(stage.SparseVoxels(feats.clone(), coords.clone(), dims, 1))
+    assert list(yb_x.spatial_shape) == list(dims) and torch.equal(yb_x.indices.cpu(), coords.cpu())
+    assert rel_err(ya.cpu(), yb_x.features.cpu()) <= 1e-4
