@@ -668,7 +668,7 @@ def run_skewed(args):
         dist.init_process_group("nccl", device_id=dev)
     steps = max(1, min(args.steps, 20))
     with ClockSampler(local) as clk:
-        sh = skewed_shard(dev, rank, world, steps=steps, warm=args.warmup,
+        sh = skewed_shard(dev, rank, world, steps=steps, warm=args.warmup, grid=args.skew_grid,
                           dtype={"bf16": torch.bfloat16, "f32": torch.float32}[args.dtype])
     peak = 1394.5
     try:
@@ -884,6 +884,8 @@ def main():
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (other dtype, "
                                                                "same-scene control, window-range shard lines)")
+    ap.add_argument("--skew-grid", type=int, default=126,
+                    help="edge of the skewed scene's grid in voxels (126 = the 10^6-voxel scene; smaller for profiler captures)")
     ap.add_argument("--workload", default="room", choices=["room", "skewed", "stage"],
                     help="room: the default line (W-MSA + SW-MSA on a 150k-voxel room); skewed: one 10^6-voxel "
                          "skewed-occupancy scene sharded by window ranges (secondary)")
