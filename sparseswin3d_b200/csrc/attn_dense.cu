@@ -42,6 +42,7 @@ constexpr int kDMaxKT = 16;    // key tiles per window at most (1024 keys)
 constexpr int kDProd = 3;      // producer warps
 constexpr int kDThreads = 384;
 constexpr int kDHalf = kDK / 2;  // keys of a tile one softmax thread looks after
+constexpr int kDOutPitch = kDRowB + 16;  // bytes between rows of the output staging tile (skewed across banks)
 constexpr int kTmemCols = 256; // S: 2 x 64 columns, O_part: 2 x 32 columns
 constexpr int kTmemS = 0, kTmemO = 128;
 
@@ -155,7 +156,7 @@ __device__ __forceinline__ uint32_t f2h2(float a, float b) {  // two floats -> p
 //   per unit (double buffered): the bias slice of its head, (2Wz-1)(2Wy-1)(2Wx-1) floats
 //   pre-multiplied by log2 e; per row of its window the voxel id, 4 x relative-position code, region
 struct DenseSmem {
-  uint32_t k, v, q, p, bias, bias_floats, vox, rel4, reg, total;
+  uint32_t k, v, q, p, bias, bias_floats, vox, rel4, reg, ostage, total;
 };
 __host__ __device__ inline DenseSmem dense_smem(int c_cap, int table_rows) {
   DenseSmem s;
@@ -169,6 +170,7 @@ __host__ __device__ inline DenseSmem dense_smem(int c_cap, int table_rows) {
   s.vox = o; o += 2u * (uint32_t)c_cap * 4u;
   s.rel4 = o; o += 2u * (uint32_t)c_cap * 4u;
   s.reg = o; o += 2u * (uint32_t)c_cap * 4u;
+  s.ostage = o; o += (uint32_t)kDQ * kDOutPitch;
   s.total = o;
   return s;
 }
@@ -193,7 +195,8 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
   uint64_t* meta_empty = meta_full + 2;        // [2]
   uint64_t* drain_bar = meta_empty + 2;        // [1]
   uint64_t* xbar = drain_bar + 1;              // [4] the two warps of a row quarter have posted their partial values
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 4);
+  uint64_t* obar = xbar + 4;                   // [1] output staging tile: written by all / read by all
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(obar + 1);
   float* xch = reinterpret_cast<float*>(smem + 1024);  // [2 buffers][2 halves][128 rows] partial maxima / sums
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = p.H, C = p.C;
@@ -224,6 +227,7 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
       mbar_init(meta_empty + b, 8);
     }
     for (int x = 0; x < 4; ++x) mbar_init(xbar + x, 2);
+    mbar_init(obar, 8);
     mbar_init(drain_bar, 1);
     mbar_fence_init();
   }
@@ -433,6 +437,7 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
       ++xn;
       return ok;
     };
+    uint32_t on = 0;  // query tiles this thread has put through the output staging tile
     for (int u = blockIdx.x; u < n_units && !timed_out; u += gridDim.x, ++un) {
       int first, c, h;
       unit_window(u, first, c, h);
@@ -556,18 +561,42 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
         // the row's sum is the two halves' sums (both were kept relative to the same running maximum)
         float l_other = 0.f;
         if (!timed_out && !exchange(l, l_other)) timed_out = true;
-        if (live && !timed_out) {
+        // The tile's output goes out through a staging tile in shared memory, so that the four lanes
+        // that write one row's 64-byte head slice sit side by side in one store instruction (a thread
+        // owns only half a slice, and its partner is in another warp).  Whole 64-byte segments matter
+        // for the destinations on peer GPUs, where every store instruction's segments cross NVLink as
+        // packets of their own.  The staging tile is guarded by one barrier of the eight softmax warps
+        // with two phases per query tile: all have written / all have read.
+        if (timed_out) break;
+        if (on > 0 && !mbar_wait_bounded(obar, 1)) { timed_out = true; break; }
+        if (live) {
           const float inv = __frcp_rn(l + l_other + 1e-8f);  // ops.cu:164
-          const int64_t off = (int64_t)wvox[qrow] * C + h * kDHD + half * (kDHD / 2);
+          const uint32_t dst = smem_u32(smem + L.ostage) + (uint32_t)row_in_tile * kDOutPitch + (uint32_t)half * (kDRowB / 2);
 #pragma unroll
           for (int e = 0; e < kDHD / 16; ++e) {
             uint32_t ww[4];
 #pragma unroll
             for (int x = 0; x < 4; ++x) ww[x] = pack2<T>(o[8 * e + 2 * x] * inv, o[8 * e + 2 * x + 1] * inv);
-            for (int d = 0; d < p.outs.n; ++d)
-              reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.outs.base[d]) + off)[e] = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+            sts_v4(dst + 16u * e, ww[0], ww[1], ww[2], ww[3]);
           }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(obar);
+        if (!mbar_wait_bounded(obar, 0)) { timed_out = true; break; }
+#pragma unroll
+        for (int k2 = 0; k2 < (kDQ * kDRowB / 16) / 256; ++k2) {
+          const int id = (int)threadIdx.x - 128 + 256 * k2;  // softmax threads are threads 128..383
+          const int orow = id >> 2, piece = id & 3;
+          if (t * kDQ + orow < c) {
+            const int4 w = lds_v4(smem_u32(smem + L.ostage) + (uint32_t)orow * kDOutPitch + 16u * piece);
+            const int64_t off = (int64_t)wvox[t * kDQ + orow] * C + h * kDHD + piece * 8;
+            for (int d = 0; d < p.outs.n; ++d)
+              *reinterpret_cast<int4*>(reinterpret_cast<T*>(p.outs.base[d]) + off) = w;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(obar);
+        ++on;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(meta_empty + mb);
