@@ -35,6 +35,8 @@ def _grads(m, feats, make_x, mask, fused, weight):
     (600, 14, 2, 16, (0, 0, 0)),    # windows above one tile (c up to ~100): the large-window items
     (900, 12, 6, 16, (3, 3, 3)),    # dense-ish, many heads
     (700, 18, 6, 16, (4, 4, 4)),    # window 9: the bias table (17^3 x 6) is too large for the shared-memory copy
+    (800, 14, 6, 32, (3, 3, 3)),    # C = 192: the pack kernel holds its pair arrays for a part of the heads at a time
+    (300, 40, 3, 32, (0, 0, 0)),    # windows of one or two voxels: packs of many windows
 ])
 def test_fused_backward_matches_unfused_chain(n_vox, grid, heads, hd, shift):
     dev = torch.device("cuda:0")
