@@ -40,8 +40,11 @@ constexpr int kDHD = 32;       // head_dim
 constexpr int kDRowB = 64;     // bytes of one q / k / v head slice (32 x 16 bit)
 constexpr int kDMaxKT = 16;    // key tiles per window at most (1024 keys)
 constexpr int kDProd = 3;      // producer warps
-constexpr int kDThreads = 384;
-constexpr int kDHalf = kDK / 2;  // keys of a tile one softmax thread looks after
+constexpr int kDParts = 2;     // softmax threads per query row, in different warps (2 or 4; measured equal)
+constexpr int kDSoftWarps = 4 * kDParts;
+constexpr int kDThreads = 128 + 32 * kDSoftWarps;
+constexpr int kDHalf = kDK / kDParts;  // keys of a tile one softmax thread looks after
+constexpr int kDCpt = kDHD / kDParts;  // output channels one softmax thread accumulates
 constexpr int kDOutPitch = kDRowB + 16;  // bytes between rows of the output staging tile (skewed across banks)
 constexpr int kTmemCols = 256; // S: 2 x 64 columns, O_part: 2 x 32 columns
 constexpr int kTmemS = 0, kTmemO = 128;
@@ -107,6 +110,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[8]) { tmem_ld8(taddr, r); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory operand descriptor (version 1): start address, leading / stride byte offsets in
@@ -150,7 +162,7 @@ __device__ __forceinline__ uint32_t f2h2(float a, float b) {  // two floats -> p
 
 // Shared memory (byte offsets from a 1024-byte aligned base):
 //   [0, 1024)        mbarriers and the tensor-memory address
-//   [1024, 3072)     partial row maxima / sums the two softmax threads of a row exchange
+//   [1024, 1024 + 2 * kDParts * 512)  partial row maxima / sums the softmax threads of a row exchange
 //   K  c_cap x 64    V  c_cap x 64    (64-byte swizzle; key tile j = rows [64 j, 64 j + 64))
 //   Q  2 x 128 x 64  (64-byte swizzle)          P  128 x 128 (128-byte swizzle) twice: P and its bf16 residual
 //   per unit (double buffered): the bias slice of its head, (2Wz-1)(2Wy-1)(2Wx-1) floats
@@ -160,7 +172,7 @@ struct DenseSmem {
 };
 __host__ __device__ inline DenseSmem dense_smem(int c_cap, int table_rows) {
   DenseSmem s;
-  uint32_t o = 3072;
+  uint32_t o = 1024u + 2u * kDParts * 512u;
   s.k = o; o += (uint32_t)c_cap * kDRowB;
   s.v = o; o += (uint32_t)c_cap * kDRowB;
   s.q = o; o += 2u * kDQ * kDRowB;
@@ -197,7 +209,7 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
   uint64_t* xbar = drain_bar + 1;              // [4] the two warps of a row quarter have posted their partial values
   uint64_t* obar = xbar + 4;                   // [1] output staging tile: written by all / read by all
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(obar + 1);
-  float* xch = reinterpret_cast<float*>(smem + 1024);  // [2 buffers][2 halves][128 rows] partial maxima / sums
+  float* xch = reinterpret_cast<float*>(smem + 1024);  // [2 buffers][kDParts][128 rows] partial maxima / sums
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = p.H, C = p.C;
 
@@ -219,15 +231,15 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
       mbar_init(q_full + b, kDProd);
       mbar_init(q_empty + b, 1);
       mbar_init(s_full + b, 1);
-      mbar_init(s_empty + b, 8);
-      mbar_init(p_full + b, 8);
+      mbar_init(s_empty + b, kDSoftWarps);
+      mbar_init(p_full + b, kDSoftWarps);
       mbar_init(pv_done + b, 1);
-      mbar_init(o_empty + b, 8);
+      mbar_init(o_empty + b, kDSoftWarps);
       mbar_init(meta_full + b, kDProd);
-      mbar_init(meta_empty + b, 8);
+      mbar_init(meta_empty + b, kDSoftWarps);
     }
-    for (int x = 0; x < 4; ++x) mbar_init(xbar + x, 2);
-    mbar_init(obar, 8);
+    for (int x = 0; x < 4; ++x) mbar_init(xbar + x, kDParts);
+    mbar_init(obar, kDSoftWarps);
     mbar_init(drain_bar, 1);
     mbar_fence_init();
   }
@@ -418,7 +430,7 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
     }
   } else {
     // =========================================== softmax rows =================================
-    const int half = (warp - 4) >> 2;          // which 32 keys of a tile / which 16 output channels
+    const int half = (warp - 4) >> 2;          // which part of a tile's keys / of the output channels (0 .. kDParts-1)
     const int sw = warp & 3;                   // tensor-memory lanes [32 sw, 32 sw + 32)
     const int row_in_tile = sw * 32 + lane;
     const uint32_t t_lane = (uint32_t)(sw * 32) << 16;
@@ -426,14 +438,21 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
     uint32_t g = 0;    // key tiles so far
     uint32_t xn = 0;   // exchanges with the partner warp so far
     int un = 0;
-    // post a value for the partner thread (same row, other half) and fetch its value
-    auto exchange = [&](float mine, float& theirs) -> bool {
-      float* slot = xch + (xn & 1) * 256;
+    // post a value for the other threads of the row (same row, other key parts) and combine theirs:
+    // the maximum of the others' values, or their sum
+    auto exchange = [&](float mine, float& theirs, bool take_max) -> bool {
+      float* slot = xch + (xn & 1) * (kDParts * 128);
       slot[half * 128 + row_in_tile] = mine;
       __syncwarp();
       if (lane == 0) mbar_arrive(xbar + sw);
       const bool ok = mbar_wait_bounded(xbar + sw, xn & 1);
-      theirs = slot[(half ^ 1) * 128 + row_in_tile];
+      float acc = take_max ? -INFINITY : 0.f;
+#pragma unroll
+      for (int o2 = 1; o2 < kDParts; ++o2) {
+        const float v = slot[((half + o2) % kDParts) * 128 + row_in_tile];
+        acc = take_max ? fmaxf(acc, v) : acc + v;
+      }
+      theirs = acc;
       ++xn;
       return ok;
     };
@@ -456,9 +475,9 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
         const uint32_t my_bias = bias_a + (uint32_t)(live ? wrel4[qrow] : 0) + (uint32_t)p.rel_off * 4u;
         const int my_region = live ? wreg[qrow] : 0;
         float m = 0.f, l = 0.f, corr_prev = 1.f;   // the maximum starts from 0 (ops.cu:137)
-        float o[kDHD / 2];
+        float o[kDCpt];
 #pragma unroll
-        for (int e = 0; e < kDHD / 2; ++e) o[e] = 0.f;
+        for (int e = 0; e < kDCpt; ++e) o[e] = 0.f;
         for (int j = 0; j <= nkt && !timed_out; ++j) {
           const uint32_t gp = g - 1, bp = gp & 1;
           if (j < nkt) {
@@ -466,8 +485,8 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
             const int nk = min(kDK, c - j * kDK) - half * kDHalf;  // valid keys among this thread's 32
             if (!mbar_wait_bounded(s_full + b, (g >> 1) & 1)) { timed_out = true; break; }
             tc_fence_after();
-            uint32_t sr[32];
-            tmem_ld32(tmem + t_lane + kTmemS + b * kDK + half * kDHalf, sr);
+            uint32_t sr[kDHalf];
+            tmem_ldn(tmem + t_lane + kTmemS + b * kDK + half * kDHalf, sr);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
@@ -503,7 +522,7 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
               mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
             float mx_other;
-            if (!exchange(mx, mx_other)) { timed_out = true; break; }
+            if (!exchange(mx, mx_other, true)) { timed_out = true; break; }
             const float m_new = fmaxf(m, fmaxf(mx, mx_other));
             const float corr = fast_exp2(m - m_new);
             m = m_new;
@@ -534,33 +553,33 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
             // fold the previous tile's O_part in with the factor its maximum update gave
             if (j > 0) {
               tc_fence_after();
-              uint32_t orr[16];
-              tmem_ld16(tmem + t_lane + kTmemO + bp * kDHD + half * (kDHD / 2), orr);
+              uint32_t orr[kDCpt];
+              tmem_ldn(tmem + t_lane + kTmemO + bp * kDHD + half * kDCpt, orr);
               tmem_ld_wait();
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(o_empty + bp);
 #pragma unroll
-              for (int e = 0; e < kDHD / 2; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(orr[e]));
+              for (int e = 0; e < kDCpt; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(orr[e]));
             }
             corr_prev = corr;
             ++g;
           } else {
             if (!mbar_wait_bounded(pv_done + bp, (gp >> 1) & 1)) { timed_out = true; break; }
             tc_fence_after();
-            uint32_t orr[16];
-            tmem_ld16(tmem + t_lane + kTmemO + bp * kDHD + half * (kDHD / 2), orr);
+            uint32_t orr[kDCpt];
+            tmem_ldn(tmem + t_lane + kTmemO + bp * kDHD + half * kDCpt, orr);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(o_empty + bp);
 #pragma unroll
-            for (int e = 0; e < kDHD / 2; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(orr[e]));
+            for (int e = 0; e < kDCpt; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(orr[e]));
           }
         }
         // the row's sum is the two halves' sums (both were kept relative to the same running maximum)
         float l_other = 0.f;
-        if (!timed_out && !exchange(l, l_other)) timed_out = true;
+        if (!timed_out && !exchange(l, l_other, false)) timed_out = true;
         // The tile's output goes out through a staging tile in shared memory, so that the four lanes
         // that write one row's 64-byte head slice sit side by side in one store instruction (a thread
         // owns only half a slice, and its partner is in another warp).  Whole 64-byte segments matter
@@ -571,9 +590,9 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
         if (on > 0 && !mbar_wait_bounded(obar, 1)) { timed_out = true; break; }
         if (live) {
           const float inv = __frcp_rn(l + l_other + 1e-8f);  // ops.cu:164
-          const uint32_t dst = smem_u32(smem + L.ostage) + (uint32_t)row_in_tile * kDOutPitch + (uint32_t)half * (kDRowB / 2);
+          const uint32_t dst = smem_u32(smem + L.ostage) + (uint32_t)row_in_tile * kDOutPitch + (uint32_t)half * (kDRowB / kDParts);
 #pragma unroll
-          for (int e = 0; e < kDHD / 16; ++e) {
+          for (int e = 0; e < kDCpt / 8; ++e) {
             uint32_t ww[4];
 #pragma unroll
             for (int x = 0; x < 4; ++x) ww[x] = pack2<T>(o[8 * e + 2 * x] * inv, o[8 * e + 2 * x + 1] * inv);
@@ -584,8 +603,8 @@ __global__ void __launch_bounds__(kDThreads, 1) k_attn_dense(DenseParams p) {
         if (lane == 0) mbar_arrive(obar);
         if (!mbar_wait_bounded(obar, 0)) { timed_out = true; break; }
 #pragma unroll
-        for (int k2 = 0; k2 < (kDQ * kDRowB / 16) / 256; ++k2) {
-          const int id = (int)threadIdx.x - 128 + 256 * k2;  // softmax threads are threads 128..383
+        for (int k2 = 0; k2 < (kDQ * kDRowB / 16) / (32 * kDSoftWarps); ++k2) {
+          const int id = (int)threadIdx.x - 128 + 32 * kDSoftWarps * k2;  // softmax threads are threads 128 and up
           const int orow = id >> 2, piece = id & 3;
           if (t * kDQ + orow < c) {
             const int4 w = lds_v4(smem_u32(smem + L.ostage) + (uint32_t)orow * kDOutPitch + 16u * piece);
