@@ -74,3 +74,25 @@ def test_gather_rows_two_gloo_ranks():
         assert p.exitcode == 0
     res = [q.get(timeout=10) for _ in range(4)]
     assert all(ok for _, ok in res)
+
+
+def test_window_range_cuts_properties_on_random_occupancies():
+    """Property test: for any occupancy list and rank count the cuts are monotone, cover every
+    window once, and no range exceeds its fair share of the estimated cost by more than one window."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.lists(st.integers(min_value=1, max_value=1023), min_size=0, max_size=400), st.integers(min_value=1, max_value=9),
+           st.sampled_from([0.0, 8.0, 32.0, 500.0]))
+    def check(occ, world, alpha):
+        counts = torch.tensor(occ, dtype=torch.int64)
+        cuts = shard.window_range_cuts(counts, world, alpha)
+        assert len(cuts) == world + 1 and cuts[0] == 0 and cuts[-1] == len(occ)
+        assert all(a <= b for a, b in zip(cuts, cuts[1:]))
+        if occ:
+            cost = shard.window_cost(counts, alpha)
+            per = [float(cost[a:b].sum()) for a, b in zip(cuts, cuts[1:])]
+            assert abs(sum(per) - float(cost.sum())) <= 1e-6 * float(cost.sum())
+            assert max(per) <= float(cost.sum()) / world + float(cost.max()) + 1e-6
+
+    check()
