@@ -741,6 +741,23 @@ def stage_line(dev, dtype_name="f32", depth=6, reps=5):
         dev_rel = float(((y.float() - ref).abs().max() / ref.abs().max()).item())
         out[name] = {"ms_per_forward": ms, "voxel_blocks_per_s": N_VOX * depth / (ms * 1e-3), "max_rel_dev_from_stage": dev_rel}
         del gr
+    # the element-wise shell kernel alone: sum = a + b and norm = LayerNorm(sum) over rotating buffers
+    # (4 sets > L2), algorithmic bytes 4 * C * elt per row (two rows in, two rows out)
+    n_sets = 6 if dtype == torch.float32 else 10
+    bufs = [(torch.randn(N_VOX, C, device=dev).to(dtype), torch.randn(N_VOX, C, device=dev).to(dtype),
+             torch.empty(N_VOX, C, device=dev, dtype=dtype)) for _ in range(n_sets)]
+    norm = layer.blocks[0].norm2
+
+    def shell(_):
+        for a_, b_, s_ in bufs:
+            stage.add_layernorm(a_, b_, norm, sum_out=s_)
+
+    sh_ms = time_graph(shell, n_sets, dev)
+    sh_bytes = 4 * C * feats.element_size() * N_VOX
+    peak, peak_src = measured_peak_gbs()
+    out["add_layernorm_kernel"] = {"us": sh_ms * 1e3, "algorithmic_bytes": sh_bytes, "achieved_gbs": sh_bytes / (sh_ms * 1e-3) / 1e9,
+                                   "frac": sh_bytes / (sh_ms * 1e-3) / 1e9 / peak, "peak": peak, "peak_source": peak_src,
+                                   "l2": f"{n_sets} rotating sets of {sh_bytes / 1e6:.0f} MB"}
     return {"workload": f"one Swin stage, depth {depth}, on the {N_VOX}-voxel room, C={C}, {HEADS} heads x {HEAD_DIM}, window 7^3, "
                         f"{dtype_name}; bucketing from raw coordinates inside every forward",
             "unit": "voxel-blocks/s", **out}

@@ -161,3 +161,22 @@ def test_stage_reuses_two_plans_and_captures_into_a_graph():
     assert "k_count" not in names and "k_scatter" not in names          # no bucketing inside the forward
     assert names.count("k_add_layernorm") > 0 and "k_attn_fused" in names
     assert all(p.stats()["error"] == 0 for p in plans)
+
+
+@pytest.mark.parametrize("n_vox", [0, 1, 3])
+def test_stage_on_almost_empty_scenes(n_vox):
+    """No voxel, one voxel, three voxels: nothing to attend to but oneself (or nobody)."""
+    from sparseswin3d_b200 import stage
+
+    dev = torch.device("cuda:0")
+    C, H, win, dims = 96, 3, (7, 7, 7), (10, 12, 9)
+    layer = stage.BasicLayer(dim=C, depth=2, num_heads=H, window_size=win, qkv_bias=True).to(dev).eval()
+    _randomise(layer, 21)
+    coords = torch.tensor([[0, 1, 2, 3], [0, 9, 11, 8], [0, 1, 2, 4]][:n_vox], dtype=torch.int32).reshape(n_vox, 4)
+    feats = torch.randn(n_vox, C, generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        y = layer(stage.SparseVoxels(feats.to(dev), coords.to(dev), dims, 1))
+    assert y.features.shape == (n_vox, C)
+    if n_vox:
+        ref = O.basic_layer(feats, coords, 1, dims, win, [_block_params(b) for b in layer.blocks], H)
+        assert rel_err(y.features.cpu(), ref) <= 2e-4
