@@ -245,6 +245,30 @@ int ssw_add_layernorm(const void* a, const void* b, const float* gamma, const fl
                       int dtype, int64_t n_rows, int32_t channels, void* sum_out, void* norm_out,
                       void* stream);
 
+/* Sparse 3-D convolutions of the layers around the attention stages (upstream takes them from the
+ * spconv library: SubMConv3d swin3d_base.py:915-923, 1039-1059; SparseConv3d :932-935, 965-970;
+ * SparseInverseConv3d :989-994).  A convolution here is a rulebook (integer kernels), a gathered
+ * operand cols[m, tap * Cin + c] = x[nbr[m, tap], c] and one dense GEMM by the host side.
+ *
+ * ssw_voxel_grid_build: grid[((b * D + z) * H + y) * W + x] = id of the voxel in that cell, -1 for an
+ *   empty cell (batch * D * H * W int32, must stay below 2^31 cells).  `err` (may be NULL): device
+ *   word that gets SSW_DEV_BAD_COORD / SSW_DEV_DUPLICATE or-ed in.
+ * ssw_subm_neighbors: nbr[i, t] for the k^3 taps of a submanifold convolution (k odd, offsets
+ *   -k/2..k/2 in z, y, x order, t = (dz * k + dy) * k + dx as a dense cross-correlation with
+ *   padding k/2 numbers them); -1 where the neighbour cell is empty or outside the grid.
+ * ssw_gather_cols: cols[m, t * cin + c] = x[nbr[m, t], c], zero where nbr < 0 (or >= n_src).
+ * ssw_gather_slices: out[i, :] = z[parent[i], tap[i] * cout : (tap[i] + 1) * cout] (z has taps * cout
+ *   columns), zero where parent[i] < 0: the scatter side of an inverse convolution whose GEMM
+ *   produced all taps of every coarse voxel at once. */
+int ssw_voxel_grid_build(const int32_t* coords, int64_t n, int32_t batch, const int32_t dims[3],
+                         int32_t* grid, int32_t* err, void* stream);
+int ssw_subm_neighbors(const int32_t* coords, int64_t n, int32_t batch, const int32_t dims[3],
+                       const int32_t* grid, int32_t ksize, int32_t* nbr, void* stream);
+int ssw_gather_cols(const void* x, int dtype, int64_t n_src, int64_t m_rows, int32_t taps, int32_t cin,
+                    const int32_t* nbr, void* cols, void* stream);
+int ssw_gather_slices(const void* z, int dtype, int64_t n_src, int32_t taps, int32_t cout, int64_t n,
+                      const int32_t* parent, const int32_t* tap, void* out, void* stream);
+
 /* Backward of ssw_attn_fused: gradients of qkv and of the bias table from the gradient of `out`,
  * with the probabilities recomputed instead of stored.  It replaces what upstream's autograd runs
  * for the same span: softmax_last_dim_backward (ops.cu:169-194, swin3d_base.py:177-188) and the

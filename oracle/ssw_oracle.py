@@ -532,3 +532,55 @@ def basic_layer(feats, coords, batch, dims, window_size, block_params, num_heads
     for i, prm in enumerate(block_params):
         x = swin_block(x, coords, batch, dims, window_size, (0, 0, 0) if i % 2 == 0 else shift, prm, num_heads, eps, acc_dtype)
     return x
+
+
+# --------------------------------------------------------------------------------------------------
+# Sparse convolutions as the dense operation restricted to the active sites (the layers upstream
+# takes from spconv: swin3d_base.py:915-935, 965-970, 989-994, 1039-1059).  Small grids only.
+# Weights in the layout of sparseswin3d_b200.sparse_conv: [k^3, Cin, Cout], tap (dz, dy, dx) at
+# (dz * k + dy) * k + dx.
+# --------------------------------------------------------------------------------------------------
+def _densify(feats, coords, batch, dims):
+    C = feats.shape[1]
+    dense = torch.zeros(batch, C, *dims, dtype=feats.dtype)
+    c = coords.long()
+    dense[c[:, 0], :, c[:, 1], c[:, 2], c[:, 3]] = feats
+    return dense
+
+
+def _dense_kernel(weight, k):
+    k3, ci, co = weight.shape
+    return weight.reshape(k, k, k, ci, co).permute(4, 3, 0, 1, 2).contiguous()   # [Cout, Cin, kz, ky, kx]
+
+
+def subm_conv3d(feats, coords, batch, dims, weight, bias=None):
+    """Submanifold convolution: conv3d with padding k // 2 on the densified scene, read at the input sites."""
+    k = round(weight.shape[0] ** (1 / 3))
+    out = torch.nn.functional.conv3d(_densify(feats, coords, batch, dims), _dense_kernel(weight, k), bias, padding=k // 2)
+    c = coords.long()
+    return out[c[:, 0], :, c[:, 1], c[:, 2], c[:, 3]]
+
+
+def strided_conv3d(feats, coords, batch, dims, weight, bias=None):
+    """kernel = stride = k, no padding: (features, coords [M,4] in (b,z,y,x) order, output dims).
+    An output cell is active when any of its k^3 input cells is."""
+    k = round(weight.shape[0] ** (1 / 3))
+    F = torch.nn.functional
+    out = F.conv3d(_densify(feats, coords, batch, dims), _dense_kernel(weight, k), bias, stride=k)
+    occ = F.max_pool3d(_densify(torch.ones(coords.shape[0], 1, dtype=feats.dtype), coords, batch, dims), k, stride=k)
+    idx = (occ[:, 0] > 0).nonzero()                       # lexicographic in (b, z, y, x)
+    return out[idx[:, 0], :, idx[:, 1], idx[:, 2], idx[:, 3]], idx.to(I32), list(out.shape[2:])
+
+
+def inverse_conv3d(feats_coarse, coords_coarse, batch, dims_coarse, coords_fine, weight, bias=None):
+    """The transposed operation of `strided_conv3d`, read at the fine sites (zero, plus bias, for a
+    fine voxel beyond the coarse grid)."""
+    k = round(weight.shape[0] ** (1 / 3))
+    k3, ci, co = weight.shape
+    wt = weight.reshape(k, k, k, ci, co).permute(3, 4, 0, 1, 2).contiguous()     # [Cin, Cout, kz, ky, kx]
+    out = torch.nn.functional.conv_transpose3d(_densify(feats_coarse, coords_coarse, batch, dims_coarse), wt, None, stride=k)
+    c = coords_fine.long()
+    res = torch.zeros(c.shape[0], co, dtype=feats_coarse.dtype)
+    ok = (c[:, 1] < out.shape[2]) & (c[:, 2] < out.shape[3]) & (c[:, 3] < out.shape[4])
+    res[ok] = out[c[ok, 0], :, c[ok, 1], c[ok, 2], c[ok, 3]]
+    return res if bias is None else res + bias

@@ -62,6 +62,10 @@ def _load() -> C.CDLL:
         "ssw_bucket_windows_static": (C.c_int, [vp, P(Geometry), vp, vp, i32, P(i32), P(PlanLayout), vp, vp]),
         "ssw_attn_fused": (C.c_int, [vp, C.c_int, i32, i32, P(PlanLayout), vp, vp, P(i32), f32, C.c_int, vp, vp, vp]),
         "ssw_attn_fused_multi": (C.c_int, [vp, C.c_int, i32, i32, P(PlanLayout), vp, vp, P(i32), f32, C.c_int, P(vp), i32, vp, vp]),
+        "ssw_voxel_grid_build": (C.c_int, [vp, i64, i32, P(i32), vp, vp, vp]),
+        "ssw_subm_neighbors": (C.c_int, [vp, i64, i32, P(i32), vp, i32, vp, vp]),
+        "ssw_gather_cols": (C.c_int, [vp, C.c_int, i64, i64, i32, i32, vp, vp, vp]),
+        "ssw_gather_slices": (C.c_int, [vp, C.c_int, i64, i32, i32, i64, vp, vp, vp, vp]),
         "ssw_add_layernorm": (C.c_int, [vp, vp, vp, vp, f32, C.c_int, i64, i32, vp, vp, vp]),
         "ssw_enable_peer_access": (C.c_int, [i32]),
         "ssw_peer_buffer_create": (C.c_int, [i64, P(vp), C.c_char_p]),

@@ -39,6 +39,7 @@ class SparseVoxels:
         self.indices = indices
         self.spatial_shape = list(spatial_shape)
         self.batch_size = int(batch_size)
+        self.indice_dict = {}          # rulebooks of the sparse convolutions, by indice_key (shared by copies)
 
     def replace_feature(self, new_features: torch.Tensor) -> "SparseVoxels":
         out = copy.copy(self)          # a new container over the same index tensor, as spconv does
