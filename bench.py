@@ -763,6 +763,82 @@ def stage_line(dev, dtype_name="f32", depth=6, reps=5):
             "unit": "voxel-blocks/s", **out}
 
 
+def conv_lines(dev, dtype_name="f32", cin=48):
+    """The sparse convolutions around the stages on the benchmark room: a 3^3 submanifold convolution
+    (cin -> cin), the 2^3 stride-2 patch merging (cin -> 2 cin) and its inverse.  Each is a rulebook
+    (built once per coordinate set), a gather kernel of this library and a library GEMM; the gather
+    is timed alone over rotating outputs and held against the HBM copy bandwidth (its algorithmic
+    bytes: the gathered operand written once + the source rows read once)."""
+    from sparseswin3d_b200 import scenes, sparse_conv, stage
+
+    dtype = {"f32": torch.float32, "bf16": torch.bfloat16}[dtype_name]
+    elt = torch.empty(0, dtype=dtype).element_size()
+    coords_np, dims = scenes.room_scene(N_VOX, seed=0)
+    coords = torch.from_numpy(coords_np).to(dev)
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = stage.SparseVoxels(torch.randn(N_VOX, cin, device=dev, generator=g).to(dtype), coords, dims, 1)
+    peak, peak_src = measured_peak_gbs()
+
+    def timed(fn, reps=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    out = {"workload": f"sparse convolutions on the {N_VOX}-voxel room ({dims[0]}x{dims[1]}x{dims[2]} cells), {dtype_name}, Cin={cin}"}
+    with torch.no_grad():
+        subm = sparse_conv.SubMConv3d(cin, cin, 3, bias=False, indice_key="s").to(dev).to(dtype)
+        down = sparse_conv.SparseConv3d(cin, 2 * cin, 2, 2, bias=False, indice_key="d").to(dev).to(dtype)
+        up = sparse_conv.SparseInverseConv3d(2 * cin, cin, 2, indice_key="d", bias=False).to(dev).to(dtype)
+        rb_ms = timed(lambda: sparse_conv.subm_rulebook(x, 3), 3)
+        rbd_ms = timed(lambda: sparse_conv.strided_rulebook(x, 2), 3)
+        y = subm(x)
+        yd = down(x)
+        rb, rbd = x.indice_dict["s"], x.indice_dict["d"]
+        # gather kernels alone: rotating outputs larger than L2
+        n_sets = 3
+        cols_sets = [torch.empty(N_VOX, 27 * cin, dtype=dtype, device=dev) for _ in range(n_sets)]
+
+        def gather_subm():
+            for c_ in cols_sets:
+                _lib_check_gather(x.features, rb.nbr, c_)
+
+        g_ms = timed(gather_subm) / n_sets
+        g_bytes = (27 * cin + cin) * elt * N_VOX
+        out["subm_3x3x3"] = {"rulebook_ms": rb_ms, "forward_ms": timed(lambda: subm(x)), "gather_kernel_ms": g_ms,
+                             "gather_algorithmic_bytes": g_bytes, "gather_gbs": g_bytes / (g_ms * 1e-3) / 1e9,
+                             "gather_frac_of_hbm": g_bytes / (g_ms * 1e-3) / 1e9 / peak, "active_neighbours_mean":
+                             float((rb.nbr >= 0).sum().item()) / N_VOX}
+        out["strided_2x2x2"] = {"rulebook_ms": rbd_ms, "forward_ms": timed(lambda: down(x)), "output_voxels": int(yd.features.shape[0])}
+        out["inverse_2x2x2"] = {"forward_ms": timed(lambda: up(yd))}
+    out["peak"] = peak
+    out["peak_source"] = peak_src
+    return out
+
+
+def _lib_check_gather(x, nbr, cols):
+    from sparseswin3d_b200._lib import check, dtype_code, lib, ptr, stream_ptr
+
+    check(lib.ssw_gather_cols(ptr(x), dtype_code(x.dtype), x.shape[0], nbr.shape[0], nbr.shape[1], x.shape[1], ptr(nbr), ptr(cols),
+                              stream_ptr(x.device)), "ssw_gather_cols")
+
+
+def run_conv(args):
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    res = {"metric": "sparse convolutions around the stages", "n_gpus": 1, "data": "synthetic",
+           "lines": [conv_lines(dev, dt, cin) for dt in ("f32", "bf16") for cin in (48, 96)]}
+    print(json.dumps(res), flush=True)
+
+
 def run_stage(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
@@ -903,7 +979,7 @@ def main():
                                                                "same-scene control, window-range shard lines)")
     ap.add_argument("--skew-grid", type=int, default=126,
                     help="edge of the skewed scene's grid in voxels (126 = the 10^6-voxel scene; smaller for profiler captures)")
-    ap.add_argument("--workload", default="room", choices=["room", "skewed", "stage"],
+    ap.add_argument("--workload", default="room", choices=["room", "skewed", "stage", "conv"],
                     help="room: the default line (W-MSA + SW-MSA on a 150k-voxel room); skewed: one 10^6-voxel "
                          "skewed-occupancy scene sharded by window ranges (secondary)")
     ap.add_argument("--blocks", type=int, default=0,
@@ -917,6 +993,8 @@ def main():
         run_skewed(args)
     elif args.workload == "stage":
         run_stage(args)
+    elif args.workload == "conv":
+        run_conv(args)
     else:
         run_ours(args)
 

@@ -37,11 +37,13 @@ def _load_upstream():
             return lambda cls: cls
 
     sp = types.ModuleType("spconv.pytorch")
-    sp.SparseModule, sp.SparseSequential = nn.Module, nn.Sequential
-    for name in ("SubMConv3d", "SparseConv3d", "SparseInverseConv3d"):
-        setattr(sp, name, type(name, (), {}))
+    from sparseswin3d_b200 import sparse_conv
     from sparseswin3d_b200.stage import SparseVoxels
 
+    # the three spconv layers and two containers upstream's shell is written against
+    sp.SubMConv3d, sp.SparseConv3d, sp.SparseInverseConv3d = (sparse_conv.SubMConv3d, sparse_conv.SparseConv3d,
+                                                              sparse_conv.SparseInverseConv3d)
+    sp.SparseModule, sp.SparseSequential = sparse_conv.SparseModule, sparse_conv.SparseSequential
     sp.SparseConvTensor = SparseVoxels      # the container upstream's blocks assert on (swin3d_base.py:338)
     spconv = types.ModuleType("spconv")
     spconv.pytorch = sp
@@ -170,3 +172,48 @@ def test_upstream_stage_and_this_stage_agree(depth):
         yb_x = theirs(stage.SparseVoxels(feats.clone(), coords.clone(), dims, 1))
     assert list(yb_x.spatial_shape) == list(dims) and torch.equal(yb_x.indices.cpu(), coords.cpu())
     assert rel_err(ya.cpu(), yb_x.features.cpu()) <= 1e-4
+
+
+def test_upstream_stage_with_patch_merging_and_patch_expand():
+    """Upstream's BasicLayer with its own PatchMerging as `downsample`, then its PatchExpand
+    (swin3d_base.py:950-1004), written against spconv's SparseConv3d / SparseInverseConv3d: here
+    those names resolve to this library's layers.  Against this package's stage + PatchMerging +
+    PatchExpand with the same weights, and against the dense operations of the oracle."""
+    import contextlib
+    import io
+
+    from oracle import ssw_oracle as O
+    from sparseswin3d_b200 import sparse_conv, stage
+    from tests.cases import make_case
+
+    up = _load_upstream()
+    dev = torch.device("cuda:0")
+    dims, win, C, H = (14, 16, 12), (7, 7, 7), 48, 3
+    case = make_case(n_vox=900, dims=dims, window=win, heads=H, head_dim=C // H, seed=77)
+    torch.manual_seed(3)
+    with contextlib.redirect_stdout(io.StringIO()):      # upstream prints the indice_key when constructing
+        theirs = up.BasicLayer(dim=C, depth=2, num_heads=H, window_size=win, drop_path=[0.0, 0.0], qkv_bias=True,
+                               downsample=up.PatchMerging, indice_key="m0").to(dev).eval()
+        theirs_up = up.PatchExpand(2 * C, indice_key="m0").to(dev).eval()
+    ours = stage.BasicLayer(dim=C, depth=2, num_heads=H, window_size=win, drop_path=[0.0, 0.0], qkv_bias=True,
+                            downsample=sparse_conv.PatchMerging, indice_key="m0").to(dev).eval()
+    ours_up = sparse_conv.PatchExpand(2 * C, indice_key="m0").to(dev).eval()
+    ours.load_state_dict(theirs.state_dict())
+    ours_up.load_state_dict(theirs_up.state_dict())
+    feats = torch.randn(900, C, device=dev)
+    coords = case["coords"].to(dev)
+    with torch.no_grad():
+        ya = ours(stage.SparseVoxels(feats, coords, dims, 1))
+        yb = theirs(stage.SparseVoxels(feats.clone(), coords, dims, 1))
+        za, zb = ours_up(ya), theirs_up(yb)
+    assert list(ya.spatial_shape) == [7, 8, 6] == list(yb.spatial_shape)
+    assert torch.equal(ya.indices, yb.indices) and ya.features.shape[1] == 2 * C
+    assert rel_err(ya.features.cpu(), yb.features.cpu()) <= 1e-4
+    assert rel_err(za.features.cpu(), zb.features.cpu()) <= 1e-4 and torch.equal(za.indices.cpu(), case["coords"])
+    # the downsampling itself against the dense convolution on the stage's output
+    blocks_out = O.basic_layer(feats.cpu(), case["coords"], 1, dims, win,
+                               [{k: v.detach().cpu() for k, v in b.state_dict().items()} for b in ours.blocks], H)
+    normed = torch.nn.functional.layer_norm(blocks_out, (C,), ours.downsample.norm.weight.detach().cpu().double(),
+                                            ours.downsample.norm.bias.detach().cpu().double(), 1e-5)
+    ref, ref_idx, _ = O.strided_conv3d(normed, case["coords"], 1, dims, ours.downsample.reduction.weight.detach().cpu().double())
+    assert torch.equal(ya.indices.cpu(), ref_idx) and rel_err(ya.features.cpu(), ref) <= 3e-4
