@@ -803,20 +803,42 @@ def conv_lines(dev, dtype_name="f32", cin=48):
         y = subm(x)
         yd = down(x)
         rb, rbd = x.indice_dict["s"], x.indice_dict["d"]
-        # gather kernels alone: rotating outputs larger than L2
+        # the kernels of the submanifold convolution alone, over rotating outputs larger than L2
         n_sets = 3
-        cols_sets = [torch.empty(N_VOX, 27 * cin, dtype=dtype, device=dev) for _ in range(n_sets)]
+        k3 = 27
+        sub = {"rulebook_ms": rb_ms, "forward_ms": timed(lambda: subm(x)), "active_neighbours_mean": float((rb.nbr >= 0).sum().item()) / N_VOX,
+               "form": "pairs grouped by tap" if rb.seg else "dense gathered operand"}
+        if rb.seg:
+            slots = (k3 - 1) * rb.seg
+            xp_sets = [torch.empty(slots, cin, dtype=dtype, device=dev) for _ in range(n_sets * 4)]
+            gp_ms = timed(lambda: [_lib_check_gather(x.features, rb.pair_in, c_) for c_ in xp_sets]) / len(xp_sets)
+            yp = torch.randn(slots, cin, device=dev).to(dtype)
+            base = torch.randn(N_VOX, cin, device=dev).to(dtype)
+            outs_ = [torch.empty(N_VOX, cin, dtype=dtype, device=dev) for _ in range(n_sets * 4)]
+            n_pairs = int((rb.pair_of >= 0).sum())
+            gp_bytes = (slots + n_pairs) * cin * elt + slots * 4    # every slot written, every pair's row read, the slot table
 
-        def gather_subm():
-            for c_ in cols_sets:
-                _lib_check_gather(x.features, rb.nbr, c_)
+            def reduce_all():
+                from sparseswin3d_b200._lib import check, dtype_code, lib, ptr, stream_ptr
+                for o_ in outs_:
+                    check(lib.ssw_gather_reduce(ptr(base), ptr(yp), dtype_code(dtype), slots, ptr(rb.pair_of), N_VOX, k3 - 1, cin,
+                                                ptr(o_), stream_ptr(dev)), "ssw_gather_reduce")
 
-        g_ms = timed(gather_subm) / n_sets
-        g_bytes = (27 * cin + cin) * elt * N_VOX
-        out["subm_3x3x3"] = {"rulebook_ms": rb_ms, "forward_ms": timed(lambda: subm(x)), "gather_kernel_ms": g_ms,
-                             "gather_algorithmic_bytes": g_bytes, "gather_gbs": g_bytes / (g_ms * 1e-3) / 1e9,
-                             "gather_frac_of_hbm": g_bytes / (g_ms * 1e-3) / 1e9 / peak, "active_neighbours_mean":
-                             float((rb.nbr >= 0).sum().item()) / N_VOX}
+            gr_ms = timed(reduce_all) / len(outs_)
+            gr_bytes = (2 * N_VOX + n_pairs) * cin * elt + N_VOX * (k3 - 1) * 4   # base in, out, the pairs' rows, the pair table
+            sub.update({"pair_slots": slots, "pairs": n_pairs, "dense_operand_rows": k3 * N_VOX,
+                        "gather_pairs_kernel": {"ms": gp_ms, "algorithmic_bytes": gp_bytes, "gbs": gp_bytes / (gp_ms * 1e-3) / 1e9,
+                                                "frac_of_hbm": gp_bytes / (gp_ms * 1e-3) / 1e9 / peak},
+                        "gather_reduce_kernel": {"ms": gr_ms, "algorithmic_bytes": gr_bytes, "gbs": gr_bytes / (gr_ms * 1e-3) / 1e9,
+                                                 "frac_of_hbm": gr_bytes / (gr_ms * 1e-3) / 1e9 / peak}})
+            del xp_sets, outs_
+        cols_sets = [torch.empty(N_VOX, k3 * cin, dtype=dtype, device=dev) for _ in range(n_sets)]
+        g_ms = timed(lambda: [_lib_check_gather(x.features, rb.nbr, c_) for c_ in cols_sets]) / n_sets
+        g_bytes = (k3 * cin + cin) * elt * N_VOX
+        sub["dense_operand_gather_kernel"] = {"ms": g_ms, "algorithmic_bytes": g_bytes, "gbs": g_bytes / (g_ms * 1e-3) / 1e9,
+                                              "frac_of_hbm": g_bytes / (g_ms * 1e-3) / 1e9 / peak}
+        del cols_sets
+        out["subm_3x3x3"] = sub
         out["strided_2x2x2"] = {"rulebook_ms": rbd_ms, "forward_ms": timed(lambda: down(x)), "output_voxels": int(yd.features.shape[0])}
         out["inverse_2x2x2"] = {"forward_ms": timed(lambda: up(yd))}
     out["peak"] = peak

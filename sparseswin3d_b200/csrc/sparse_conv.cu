@@ -12,6 +12,8 @@
 // The rulebook of a submanifold convolution comes from a dense cell -> voxel-id table of the scene
 // (4 bytes per cell of the grid: 96 MB for 400 x 400 x 150, independent of the channel count and
 // shared by every layer over the same coordinates).
+#include <type_traits>
+
 #include "ssw_common.cuh"
 
 namespace ssw {
@@ -105,6 +107,63 @@ __global__ void k_gather_slices(const unsigned char* __restrict__ z, int64_t n, 
   }
 }
 
+// out[i, :] = base[i, :] + sum_t y[pair[i, t], :] over the taps with pair[i, t] >= 0, summed in fp32
+// in tap order (deterministic).  One thread per (row, 8-byte or 16-byte chunk).
+template <typename T>
+__global__ void k_gather_reduce(const T* __restrict__ base, const T* __restrict__ y, int64_t n_y,
+                                const int32_t* __restrict__ pair, int64_t n, int taps, int c, T* __restrict__ out) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const int chunks = c / V;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * chunks) return;
+  const int64_t i = idx / chunks;
+  const int ch = (int)(idx - i * chunks);
+  float acc[V];
+  auto add = [&](const T* row) {
+    if constexpr (sizeof(T) == 4) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(row) + ch);
+      acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+    } else {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(row) + ch);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+          acc[2 * k] += __uint_as_float(w[k] << 16);
+          acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+        } else {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+          acc[2 * k] += f.x;
+          acc[2 * k + 1] += f.y;
+        }
+      }
+    }
+  };
+#pragma unroll
+  for (int k = 0; k < V; ++k) acc[k] = 0.f;
+  if (base) add(base + i * c);
+  for (int t = 0; t < taps; ++t) {
+    const int pj = __ldg(pair + i * taps + t);
+    if ((unsigned)pj < (unsigned)n_y) add(y + (int64_t)pj * c);
+  }
+  if constexpr (sizeof(T) == 4) {
+    reinterpret_cast<float4*>(out + i * c)[ch] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+        w[k] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = __floats2half2_rn(acc[2 * k], acc[2 * k + 1]);
+        w[k] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    reinterpret_cast<uint4*>(out + i * c)[ch] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 static int vec_of(int row_bytes, const void* a, const void* b) {
   const uintptr_t al = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b);
   if (row_bytes % 16 == 0 && (al & 15) == 0) return 16;
@@ -184,5 +243,36 @@ extern "C" int ssw_gather_slices(const void* z, int dtype, int64_t n_src, int32_
   else if (vec == 4) k_gather_slices<4><<<blocks, 256, 0, stream>>>(zs, n, out_bytes, zrb, parent, tap, n_src, taps, os);
   else k_gather_slices<2><<<blocks, 256, 0, stream>>>(zs, n, out_bytes, zrb, parent, tap, n_src, taps, os);
   SSW_LAUNCH_CHECK("k_gather_slices");
+  return SSW_OK;
+}
+
+extern "C" int ssw_gather_reduce(const void* base, const void* y, int dtype, int64_t n_y, const int32_t* pair, int64_t n,
+                                 int32_t taps, int32_t c, void* out, void* stream_) {
+  const int elt = elt_of(dtype);
+  if (!elt || n < 0 || n_y < 0 || taps < 0 || c <= 0) return SSW_E_INVALID;
+  if (n == 0) return SSW_OK;
+  if (!out || (taps > 0 && (!pair || (n_y > 0 && !y)))) return SSW_E_INVALID;
+  if ((c * elt) % 16) return SSW_E_UNSUPPORTED;
+  const void* ptrs[3] = {base, y, out};
+  for (const void* q : ptrs)
+    if (q && (reinterpret_cast<uintptr_t>(q) & 15)) return SSW_E_INVALID;
+  const int64_t total = n * (c * elt / 16);
+  const unsigned blocks = (unsigned)ceil_div64(total, 256);
+  cudaStream_t stream = (cudaStream_t)stream_;
+  switch (dtype) {
+    case SSW_F32:
+      k_gather_reduce<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(base), reinterpret_cast<const float*>(y),
+                                                         n_y, pair, n, taps, c, reinterpret_cast<float*>(out));
+      break;
+    case SSW_BF16:
+      k_gather_reduce<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(base),
+                                                                 reinterpret_cast<const __nv_bfloat16*>(y), n_y, pair, n, taps, c,
+                                                                 reinterpret_cast<__nv_bfloat16*>(out));
+      break;
+    default:
+      k_gather_reduce<__half><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __half*>(base), reinterpret_cast<const __half*>(y),
+                                                          n_y, pair, n, taps, c, reinterpret_cast<__half*>(out));
+  }
+  SSW_LAUNCH_CHECK("k_gather_reduce");
   return SSW_OK;
 }

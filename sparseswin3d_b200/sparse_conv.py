@@ -6,7 +6,9 @@ operating on `stage.SparseVoxels` (or any object with `features`, `indices` [N,4
 
 A convolution is a rulebook (which input voxel feeds which output voxel through which kernel tap,
 built once per `indice_key` and kept in `x.indice_dict`), a gathered operand (this library's
-kernels) and one dense GEMM (torch).  Semantics are those of the dense operation restricted to the
+kernels) and one dense GEMM (torch).  A submanifold convolution over a sparse neighbourhood takes
+the pair form instead: the existing (input, output) pairs grouped by tap, one batched GEMM over the
+taps, and a gather-reduce on the output side.  Semantics are those of the dense operation restricted to the
 active sites:
 
 * `SubMConv3d(k, padding=k//2)`: output sites = input sites in the same order;
@@ -37,6 +39,9 @@ from ._lib import check, dtype_code, lib, ptr, stream_ptr
 from .stage import SparseVoxels
 
 I32 = torch.int32
+# the pair form of a submanifold convolution is used when its padded pair slots are at most this
+# fraction of the dense operand's k^3 N rows
+PAIR_FORM_MAX_FILL = 0.5
 
 
 @dataclass
@@ -50,6 +55,11 @@ class Rulebook:
     nbr: torch.Tensor             # [M, k^3] int32: input voxel per (output voxel, tap), -1 = none
     parent: Optional[torch.Tensor] = None   # strided: [N] output voxel of every input voxel, -1 = none
     tap: Optional[torch.Tensor] = None      # strided: [N] tap through which it feeds its parent
+    # subm, pair form (only when the scene is sparse enough for it to pay): the off-centre taps'
+    # (input, output) pairs grouped by tap, every tap's run padded to `seg` entries
+    seg: int = 0
+    pair_in: Optional[torch.Tensor] = None  # [(k^3 - 1) * seg, 1] input voxel of every pair slot, -1 = padding
+    pair_of: Optional[torch.Tensor] = None  # [N, k^3 - 1] pair slot that feeds output i through tap t, -1 = none
 
 
 def _dims3(d: Sequence[int]):
@@ -82,7 +92,28 @@ def subm_rulebook(x, ksize: int) -> Rulebook:
     nbr = torch.empty((n, ksize ** 3), dtype=I32, device=x.indices.device)
     check(lib.ssw_subm_neighbors(ptr(x.indices), n, int(x.batch_size), _dims3(x.spatial_shape), ptr(grid), int(ksize), ptr(nbr),
                                  stream_ptr(x.indices.device)), "ssw_subm_neighbors")
-    return Rulebook("subm", ksize, x.indices, list(x.spatial_shape), x.indices, list(x.spatial_shape), nbr)
+    rb = Rulebook("subm", ksize, x.indices, list(x.spatial_shape), x.indices, list(x.spatial_shape), nbr)
+    # Pair form.  On a surface-sparse scene a voxel has a few of its k^3 neighbours, and the gathered
+    # operand [N, k^3 Cin] would be mostly zeros.  Group the existing (input, output) pairs by tap
+    # instead, pad every off-centre tap's run to the longest one (so that one batched GEMM serves
+    # them all) and let the output side pick its pairs up (`ssw_gather_reduce`).  One read-back.
+    k3 = ksize ** 3
+    if n > 0 and k3 > 1:
+        centre = k3 // 2
+        off = torch.cat([nbr[:, :centre], nbr[:, centre + 1:]], 1).t().contiguous()   # [k^3 - 1, N], tap-major
+        has = off >= 0
+        rank = torch.cumsum(has, 1, dtype=torch.int32) - 1                   # position inside its tap's run
+        seg = int(rank[:, -1].max()) + 1
+        seg = (seg + 7) // 8 * 8
+        if 0 < (k3 - 1) * seg <= PAIR_FORM_MAX_FILL * k3 * n:
+            taps = torch.arange(k3 - 1, dtype=torch.int32, device=nbr.device).unsqueeze(1)
+            slot = taps * seg + rank
+            rb.pair_of = torch.where(has, slot, torch.full_like(slot, -1)).t().contiguous()   # [N, k^3 - 1]
+            pair_in = torch.full(((k3 - 1) * seg,), -1, dtype=I32, device=nbr.device)
+            pair_in[slot[has].long()] = off[has]
+            rb.pair_in = pair_in.view(-1, 1)
+            rb.seg = seg
+    return rb
 
 
 def strided_rulebook(x, ksize: int) -> Rulebook:
@@ -206,8 +237,24 @@ class SubMConv3d(_ConvBase):
 
     def forward(self, x):
         rb = self._rulebook(x, "subm", subm_rulebook)
-        cols = gather_cols(x.features, rb.nbr)
-        return x.replace_feature(self._affine(cols, self.weight.reshape(-1, self.out_channels)))
+        f = x.features
+        pairs_ok = (rb.seg > 0 and not (torch.is_grad_enabled() and (f.requires_grad or self.weight.requires_grad))
+                    and (self.out_channels * f.element_size()) % 16 == 0)
+        if not pairs_ok:
+            cols = gather_cols(f, rb.nbr)
+            return x.replace_feature(self._affine(cols, self.weight.reshape(-1, self.out_channels)))
+        k3 = self.kernel_size ** 3
+        centre = k3 // 2
+        w = self.weight.to(f.dtype)
+        base = f @ w[centre]                                                 # the voxel itself
+        if self.bias is not None:
+            base = base + self.bias.to(base.dtype)
+        xp = gather_cols(f, rb.pair_in).view(k3 - 1, rb.seg, self.in_channels)
+        yp = torch.bmm(xp, torch.cat([w[:centre], w[centre + 1:]], 0)).view(-1, self.out_channels)
+        out = torch.empty_like(base)
+        check(lib.ssw_gather_reduce(ptr(base), ptr(yp), dtype_code(f.dtype), yp.shape[0], ptr(rb.pair_of), f.shape[0], k3 - 1,
+                                    self.out_channels, ptr(out), stream_ptr(f.device)), "ssw_gather_reduce")
+        return x.replace_feature(out)
 
 
 class SparseConv3d(_ConvBase):

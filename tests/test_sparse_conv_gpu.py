@@ -16,11 +16,15 @@ def _scene(dims, batch, n_vox, seed):
     return case["coords"]
 
 
+@pytest.mark.parametrize("pair_form", [True, False])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("dims,batch,cin,cout", [((9, 10, 11), 2, 6, 16), ((12, 12, 12), 1, 48, 48), ((7, 16, 5), 1, 16, 24)])
-def test_submanifold_conv_against_dense(dims, batch, cin, cout, dtype):
+def test_submanifold_conv_against_dense(dims, batch, cin, cout, dtype, pair_form, monkeypatch):
+    """Both forms of the submanifold convolution: pairs grouped by tap + gather-reduce (sparse
+    neighbourhoods) and the dense gathered operand."""
     from sparseswin3d_b200 import sparse_conv, stage
 
+    monkeypatch.setattr(sparse_conv, "PAIR_FORM_MAX_FILL", 1.0 if pair_form else 0.0)
     dev = torch.device("cuda:0")
     coords = _scene(dims, batch, 300, sum(dims))
     g = torch.Generator().manual_seed(cin)
@@ -31,6 +35,7 @@ def test_submanifold_conv_against_dense(dims, batch, cin, cout, dtype):
         y = conv(x)
         y2 = conv(y.replace_feature(x.features))          # second layer on the same key: rulebook reused
     assert y.indices is x.indices and "k" in x.indice_dict and torch.equal(y.features, y2.features)
+    assert (x.indice_dict["k"].seg > 0) == pair_form
     ref = O.subm_conv3d(feats.double(), coords, batch, dims, conv.weight.detach().cpu().double(), conv.bias.detach().cpu().double())
     assert rel_err(y.features.float().cpu(), ref) <= TOL[dtype]
     # the rulebook itself, bit exact: neighbour ids from a dictionary of the coordinates
