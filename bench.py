@@ -815,17 +815,17 @@ def conv_lines(dev, dtype_name="f32", cin=48):
             yp = torch.randn(slots, cin, device=dev).to(dtype)
             base = torch.randn(N_VOX, cin, device=dev).to(dtype)
             outs_ = [torch.empty(N_VOX, cin, dtype=dtype, device=dev) for _ in range(n_sets * 4)]
-            n_pairs = int((rb.pair_of >= 0).sum())
+            n_pairs = int(rb.row_slots.shape[0])
             gp_bytes = (slots + n_pairs) * cin * elt + slots * 4    # every slot written, every pair's row read, the slot table
 
             def reduce_all():
                 from sparseswin3d_b200._lib import check, dtype_code, lib, ptr, stream_ptr
                 for o_ in outs_:
-                    check(lib.ssw_gather_reduce(ptr(base), ptr(yp), dtype_code(dtype), slots, ptr(rb.pair_of), N_VOX, k3 - 1, cin,
-                                                ptr(o_), stream_ptr(dev)), "ssw_gather_reduce")
+                    check(lib.ssw_gather_reduce(ptr(base), ptr(yp), dtype_code(dtype), slots, ptr(rb.row_start), ptr(rb.row_slots),
+                                                n_pairs, N_VOX, cin, ptr(o_), stream_ptr(dev)), "ssw_gather_reduce")
 
             gr_ms = timed(reduce_all) / len(outs_)
-            gr_bytes = (2 * N_VOX + n_pairs) * cin * elt + N_VOX * (k3 - 1) * 4   # base in, out, the pairs' rows, the pair table
+            gr_bytes = (2 * N_VOX + n_pairs) * cin * elt + (N_VOX + n_pairs) * 4   # base in, out, the pairs' rows, the row lists
             sub.update({"pair_slots": slots, "pairs": n_pairs, "dense_operand_rows": k3 * N_VOX,
                         "gather_pairs_kernel": {"ms": gp_ms, "algorithmic_bytes": gp_bytes, "gbs": gp_bytes / (gp_ms * 1e-3) / 1e9,
                                                 "frac_of_hbm": gp_bytes / (gp_ms * 1e-3) / 1e9 / peak},

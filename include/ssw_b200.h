@@ -260,10 +260,10 @@ int ssw_add_layernorm(const void* a, const void* b, const float* gamma, const fl
  * ssw_gather_slices: out[i, :] = z[parent[i], tap[i] * cout : (tap[i] + 1) * cout] (z has taps * cout
  *   columns), zero where parent[i] < 0: the scatter side of an inverse convolution whose GEMM
  *   produced all taps of every coarse voxel at once.
- * ssw_gather_reduce: out[i, :] = base[i, :] + sum over t of y[pair[i, t], :] for pair[i, t] >= 0 (base may
- *   be NULL), summed in fp32 in tap order: the output side of a convolution whose products were
- *   formed only for the (input, output) pairs that exist, grouped by tap.  c * element size a
- *   multiple of 16. */
+ * ssw_gather_reduce: out[i, :] = base[i, :] + sum of y[slots[p], :] over p in [row_start[i], row_start[i+1])
+ *   (base may be NULL; row_start has n + 1 entries), summed in fp32 in list order: the output side of
+ *   a convolution whose products were formed only for the (input, output) pairs that exist,
+ *   grouped by tap.  c * element size a multiple of 16. */
 int ssw_voxel_grid_build(const int32_t* coords, int64_t n, int32_t batch, const int32_t dims[3],
                          int32_t* grid, int32_t* err, void* stream);
 int ssw_subm_neighbors(const int32_t* coords, int64_t n, int32_t batch, const int32_t dims[3],
@@ -272,8 +272,8 @@ int ssw_gather_cols(const void* x, int dtype, int64_t n_src, int64_t m_rows, int
                     const int32_t* nbr, void* cols, void* stream);
 int ssw_gather_slices(const void* z, int dtype, int64_t n_src, int32_t taps, int32_t cout, int64_t n,
                       const int32_t* parent, const int32_t* tap, void* out, void* stream);
-int ssw_gather_reduce(const void* base, const void* y, int dtype, int64_t n_y, const int32_t* pair,
-                      int64_t n, int32_t taps, int32_t c, void* out, void* stream);
+int ssw_gather_reduce(const void* base, const void* y, int dtype, int64_t n_y, const int32_t* row_start,
+                      const int32_t* slots, int64_t n_slots, int64_t n, int32_t c, void* out, void* stream);
 
 /* Backward of ssw_attn_fused: gradients of qkv and of the bias table from the gradient of `out`,
  * with the probabilities recomputed instead of stored.  It replaces what upstream's autograd runs

@@ -65,7 +65,7 @@ def _load() -> C.CDLL:
         "ssw_voxel_grid_build": (C.c_int, [vp, i64, i32, P(i32), vp, vp, vp]),
         "ssw_subm_neighbors": (C.c_int, [vp, i64, i32, P(i32), vp, i32, vp, vp]),
         "ssw_gather_cols": (C.c_int, [vp, C.c_int, i64, i64, i32, i32, vp, vp, vp]),
-        "ssw_gather_reduce": (C.c_int, [vp, vp, C.c_int, i64, vp, i64, i32, i32, vp, vp]),
+        "ssw_gather_reduce": (C.c_int, [vp, vp, C.c_int, i64, vp, vp, i64, i64, i32, vp, vp]),
         "ssw_gather_slices": (C.c_int, [vp, C.c_int, i64, i32, i32, i64, vp, vp, vp, vp]),
         "ssw_add_layernorm": (C.c_int, [vp, vp, vp, vp, f32, C.c_int, i64, i32, vp, vp, vp]),
         "ssw_enable_peer_access": (C.c_int, [i32]),

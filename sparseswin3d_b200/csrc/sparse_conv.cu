@@ -107,11 +107,12 @@ __global__ void k_gather_slices(const unsigned char* __restrict__ z, int64_t n, 
   }
 }
 
-// out[i, :] = base[i, :] + sum_t y[pair[i, t], :] over the taps with pair[i, t] >= 0, summed in fp32
-// in tap order (deterministic).  One thread per (row, 8-byte or 16-byte chunk).
+// out[i, :] = base[i, :] + sum of y[slots[p], :] over p in [row_start[i], row_start[i + 1]), summed in
+// fp32 in list order (deterministic).  One thread per (row, 16-byte chunk).
 template <typename T>
 __global__ void k_gather_reduce(const T* __restrict__ base, const T* __restrict__ y, int64_t n_y,
-                                const int32_t* __restrict__ pair, int64_t n, int taps, int c, T* __restrict__ out) {
+                                const int32_t* __restrict__ row_start, const int32_t* __restrict__ slots, int64_t n_slots,
+                                int64_t n, int c, T* __restrict__ out) {
   constexpr int V = 16 / (int)sizeof(T);
   const int chunks = c / V;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -142,8 +143,10 @@ __global__ void k_gather_reduce(const T* __restrict__ base, const T* __restrict_
 #pragma unroll
   for (int k = 0; k < V; ++k) acc[k] = 0.f;
   if (base) add(base + i * c);
-  for (int t = 0; t < taps; ++t) {
-    const int pj = __ldg(pair + i * taps + t);
+  // a list that does not fit its own table (a stale or foreign rulebook) is cut to the table
+  const int64_t p0 = max(0, __ldg(row_start + i)), p1 = min((int64_t)__ldg(row_start + i + 1), n_slots);
+  for (int64_t q = p0; q < p1; ++q) {
+    const int pj = __ldg(slots + q);
     if ((unsigned)pj < (unsigned)n_y) add(y + (int64_t)pj * c);
   }
   if constexpr (sizeof(T) == 4) {
@@ -246,12 +249,12 @@ extern "C" int ssw_gather_slices(const void* z, int dtype, int64_t n_src, int32_
   return SSW_OK;
 }
 
-extern "C" int ssw_gather_reduce(const void* base, const void* y, int dtype, int64_t n_y, const int32_t* pair, int64_t n,
-                                 int32_t taps, int32_t c, void* out, void* stream_) {
+extern "C" int ssw_gather_reduce(const void* base, const void* y, int dtype, int64_t n_y, const int32_t* row_start,
+                                 const int32_t* slots, int64_t n_slots, int64_t n, int32_t c, void* out, void* stream_) {
   const int elt = elt_of(dtype);
-  if (!elt || n < 0 || n_y < 0 || taps < 0 || c <= 0) return SSW_E_INVALID;
+  if (!elt || n < 0 || n_y < 0 || n_slots < 0 || c <= 0) return SSW_E_INVALID;
   if (n == 0) return SSW_OK;
-  if (!out || (taps > 0 && (!pair || (n_y > 0 && !y)))) return SSW_E_INVALID;
+  if (!out || !row_start || (n_slots > 0 && (!slots || !y))) return SSW_E_INVALID;
   if ((c * elt) % 16) return SSW_E_UNSUPPORTED;
   const void* ptrs[3] = {base, y, out};
   for (const void* q : ptrs)
@@ -262,16 +265,16 @@ extern "C" int ssw_gather_reduce(const void* base, const void* y, int dtype, int
   switch (dtype) {
     case SSW_F32:
       k_gather_reduce<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(base), reinterpret_cast<const float*>(y),
-                                                         n_y, pair, n, taps, c, reinterpret_cast<float*>(out));
+                                                         n_y, row_start, slots, n_slots, n, c, reinterpret_cast<float*>(out));
       break;
     case SSW_BF16:
       k_gather_reduce<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(base),
-                                                                 reinterpret_cast<const __nv_bfloat16*>(y), n_y, pair, n, taps, c,
-                                                                 reinterpret_cast<__nv_bfloat16*>(out));
+                                                                 reinterpret_cast<const __nv_bfloat16*>(y), n_y, row_start, slots,
+                                                                 n_slots, n, c, reinterpret_cast<__nv_bfloat16*>(out));
       break;
     default:
       k_gather_reduce<__half><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __half*>(base), reinterpret_cast<const __half*>(y),
-                                                          n_y, pair, n, taps, c, reinterpret_cast<__half*>(out));
+                                                          n_y, row_start, slots, n_slots, n, c, reinterpret_cast<__half*>(out));
   }
   SSW_LAUNCH_CHECK("k_gather_reduce");
   return SSW_OK;

@@ -56,10 +56,11 @@ class Rulebook:
     parent: Optional[torch.Tensor] = None   # strided: [N] output voxel of every input voxel, -1 = none
     tap: Optional[torch.Tensor] = None      # strided: [N] tap through which it feeds its parent
     # subm, pair form (only when the scene is sparse enough for it to pay): the off-centre taps'
-    # (input, output) pairs grouped by tap, every tap's run padded to `seg` entries
+    # (input, output) pairs grouped by tap, every tap's run padded to `seg` slots
     seg: int = 0
     pair_in: Optional[torch.Tensor] = None  # [(k^3 - 1) * seg, 1] input voxel of every pair slot, -1 = padding
-    pair_of: Optional[torch.Tensor] = None  # [N, k^3 - 1] pair slot that feeds output i through tap t, -1 = none
+    row_start: Optional[torch.Tensor] = None   # [N + 1] output i's pair slots are row_slots[row_start[i] : row_start[i + 1]]
+    row_slots: Optional[torch.Tensor] = None   # [pairs] in tap order within a row
 
 
 def _dims3(d: Sequence[int]):
@@ -108,10 +109,15 @@ def subm_rulebook(x, ksize: int) -> Rulebook:
         if 0 < (k3 - 1) * seg <= PAIR_FORM_MAX_FILL * k3 * n:
             taps = torch.arange(k3 - 1, dtype=torch.int32, device=nbr.device).unsqueeze(1)
             slot = taps * seg + rank
-            rb.pair_of = torch.where(has, slot, torch.full_like(slot, -1)).t().contiguous()   # [N, k^3 - 1]
             pair_in = torch.full(((k3 - 1) * seg,), -1, dtype=I32, device=nbr.device)
             pair_in[slot[has].long()] = off[has]
             rb.pair_in = pair_in.view(-1, 1)
+            # the same pairs seen from the output side: per output row the list of its slots, in tap order
+            has_rt = has.t().contiguous()                                     # [N, k^3 - 1]
+            rb.row_slots = slot.t()[has_rt].to(I32).contiguous()
+            row_start = torch.zeros(n + 1, dtype=I32, device=nbr.device)
+            row_start[1:] = torch.cumsum(has_rt.sum(1, dtype=torch.int32), 0, dtype=torch.int32)
+            rb.row_start = row_start
             rb.seg = seg
     return rb
 
@@ -252,8 +258,9 @@ class SubMConv3d(_ConvBase):
         xp = gather_cols(f, rb.pair_in).view(k3 - 1, rb.seg, self.in_channels)
         yp = torch.bmm(xp, torch.cat([w[:centre], w[centre + 1:]], 0)).view(-1, self.out_channels)
         out = torch.empty_like(base)
-        check(lib.ssw_gather_reduce(ptr(base), ptr(yp), dtype_code(f.dtype), yp.shape[0], ptr(rb.pair_of), f.shape[0], k3 - 1,
-                                    self.out_channels, ptr(out), stream_ptr(f.device)), "ssw_gather_reduce")
+        check(lib.ssw_gather_reduce(ptr(base), ptr(yp), dtype_code(f.dtype), yp.shape[0], ptr(rb.row_start), ptr(rb.row_slots),
+                                    rb.row_slots.shape[0], f.shape[0], self.out_channels, ptr(out), stream_ptr(f.device)),
+              "ssw_gather_reduce")
         return x.replace_feature(out)
 
 
