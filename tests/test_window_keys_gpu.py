@@ -106,3 +106,38 @@ def test_fused_attention_on_clamped_and_partly_shifted_grids(dims, win, shift, b
         chain, _ = O.window_attention_core(case["qkv"], case["indices"], case["n_windows"], case["n"], case["scale"],
                                            case["table"], case["rpi"], case["mask"])
         assert rel_err(out.cpu(), chain) <= tol
+
+
+def test_random_geometries_bit_exact():
+    """A seeded sweep over random grids, windows, shifts and batch sizes: window keys, region ids and
+    the sorted permutation against the oracle / a host sort of the same keys, bit for bit."""
+    from sparseswin3d_b200 import attention, window
+
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(2024)
+    for trial in range(24):
+        dims = tuple(int(v) for v in rng.integers(4, 36, 3))
+        win = tuple(int(v) for v in rng.integers(3, 10, 3))
+        shift = tuple(int(rng.integers(0, w // 2 + 1)) for w in win)
+        batch = int(rng.integers(1, 4))
+        n_vox = int(min(rng.integers(1, 1500), dims[0] * dims[1] * dims[2]))
+        case = make_case(n_vox=n_vox, dims=dims, window=win, shift=shift, batch=batch, seed=1000 + trial)
+        geom = window.resolve_geometry(batch, dims, win, shift)
+        coords = case["coords"].to(dev)
+        idx, region, err = window.window_keys(coords, geom, with_region=True)
+        assert int(err) == 0 and torch.equal(idx.cpu(), case["indices"]), (dims, win, shift, batch)
+        if case["mask"] is not None:
+            assert torch.equal(region.cpu(), _oracle_regions(case)), (dims, win, shift, batch)
+        else:
+            assert int(region.abs().max()) == 0
+        plan = window.bucket_windows(coords=coords, geom=geom, **attention.plan_params(3, 32, torch.float32, win))
+        st = plan.stats()
+        assert st["error"] == 0 and st["voxels"] == coords.shape[0]
+        key = case["indices"][:, 0].long() * case["n"] + case["indices"][:, 1].long()
+        want_perm = torch.argsort(key, stable=True)
+        assert torch.equal(plan.perm.cpu().long(), want_perm), (dims, win, shift, batch)
+        inv = torch.empty_like(want_perm)
+        inv[want_perm] = torch.arange(want_perm.numel())
+        assert torch.equal(plan.inv_perm.cpu().long(), inv)
+        counts = torch.unique(case["indices"][:, 0], return_counts=True)[1]
+        assert torch.equal(plan.occupancy().cpu().long(), counts) and st["windows"] == counts.numel()
