@@ -114,10 +114,33 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_inputs(seed: int, dtype: torch.dtype, device, n_sets: int):
+def room_variant(variant: int):
+    """The benchmark room (seed 0) under the `variant`-th symmetry of its 400 x 400 floor plan (flips of
+    the two long axes and their transposition: 8 scenes with different coordinates, the same voxel
+    count and, within 0.4 %, the same window occupancies - sum c^2 1.767-1.773 M unshifted,
+    1.681-1.698 M shifted - where rooms drawn from different seeds differ by up to 13 %).  Weak scaling
+    wants the work per GPU fixed; rank r takes variant r % 8."""
+    import numpy as np
+
     from sparseswin3d_b200 import scenes
 
-    coords, dims = scenes.room_scene(N_VOX, seed=seed)
+    coords, dims = scenes.room_scene(N_VOX, seed=0)
+    k = variant % 8
+    a, b = coords[:, 1].copy(), coords[:, 2].copy()
+    assert dims[0] == dims[1]
+    if k & 4:
+        a, b = b, a
+    if k & 1:
+        a = dims[0] - 1 - a
+    if k & 2:
+        b = dims[1] - 1 - b
+    out = coords.copy()
+    out[:, 1], out[:, 2] = a, b
+    return np.ascontiguousarray(out), dims
+
+
+def make_inputs(seed: int, dtype: torch.dtype, device, n_sets: int):
+    coords, dims = room_variant(seed)
     g = torch.Generator().manual_seed(1000 + seed)
     qkv_host = [torch.randn(N_VOX, 3, HEADS, HEAD_DIM, generator=g).to(dtype).pin_memory() for _ in range(n_sets)]
     coords_host = torch.from_numpy(coords).pin_memory()
@@ -496,7 +519,8 @@ def run_ours(args):
                    "c_max": st["c_max"], "tile_rows": rs.pp["tile_rows"],
                    "l2": f"{rs.N_SETS} rotating qkv/out sets ({rs.N_SETS * roof['algorithmic_bytes'] / 1e6:.0f} MB) > 126 MB L2; "
                          "the two passes of a step and consecutive steps use different sets",
-                   "parallelism": f"scene per GPU x{world}",
+                   "parallelism": f"scene per GPU x{world}: rank r runs the seed-0 room under the r-th symmetry of its floor plan "
+                                  "(distinct coordinates, equal work); control_same_scene: every rank on variant 0",
                    "launch": "one CUDA graph replay per step; the SW-MSA plan is built on a second stream beside the W-MSA pass"},
         "timing": {"blocks": n_blocks, "steps_per_block": args.steps, "block_ms_min": min(job_blocks),
                    "block_ms_median": ms, "block_ms_max": max(job_blocks),
