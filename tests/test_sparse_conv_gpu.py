@@ -114,3 +114,56 @@ def test_patch_merging_and_expand_round_trip_shapes():
     uniq = torch.unique(torch.cat([coords[:, :1], coords[:, 1:] // 2], 1), dim=0)
     assert torch.equal(y.indices.cpu(), uniq.to(torch.int32))         # unique(coords // 2), sorted
     assert z.features.shape == (coords.shape[0], 48) and z.indices is x.indices
+
+
+def test_full_size_room_properties(monkeypatch):
+    """150 000-voxel room, where the dense oracle cannot go: the two forms of the submanifold
+    convolution agree with each other, a centre-only kernel is a plain Linear, the rulebook is
+    symmetric, and the strided convolution / its inverse conserve what they must."""
+    from sparseswin3d_b200 import scenes, sparse_conv, stage
+
+    dev = torch.device("cuda:0")
+    coords_np, dims = scenes.room_scene(150_000, seed=0)
+    coords = torch.from_numpy(coords_np).to(dev)
+    n, C = coords.shape[0], 48
+    g = torch.Generator(device=dev).manual_seed(4)
+    feats = torch.randn(n, C, device=dev, generator=g)
+    conv = sparse_conv.SubMConv3d(C, C, 3, bias=False, indice_key="a").to(dev)
+    with torch.no_grad():
+        x = stage.SparseVoxels(feats, coords, dims, 1)
+        y_pairs = conv(x).features
+        assert x.indice_dict["a"].seg > 0                               # the room is sparse: pair form
+        monkeypatch.setattr(sparse_conv, "PAIR_FORM_MAX_FILL", 0.0)
+        x2 = stage.SparseVoxels(feats, coords, dims, 1)
+        y_dense = conv(x2).features
+        assert x2.indice_dict["a"].seg == 0
+        assert rel_err(y_pairs.cpu(), y_dense.cpu()) <= 1e-5
+        # neighbour relation is symmetric: j is i's neighbour through tap t  <=>  i is j's through 26 - t
+        nbr = x2.indice_dict["a"].nbr
+        i = torch.randint(0, n, (4000,), device=dev, generator=g)
+        t = torch.randint(0, 27, (4000,), device=dev, generator=g)
+        j = nbr[i, t].long()
+        ok = j >= 0
+        assert torch.equal(nbr[j[ok], 26 - t[ok]].long(), i[ok])
+        assert torch.equal(nbr[:, 13].long(), torch.arange(n, device=dev))   # the centre tap is the voxel itself
+        # a kernel with only its centre tap is a Linear over the channels
+        w = torch.zeros_like(conv.weight)
+        w[13] = conv.weight[13]
+        conv.weight.copy_(w)
+        assert rel_err(conv(x).features.cpu(), (feats @ w[13]).cpu()) <= 1e-5
+        # strided convolution with every tap the identity: each output is the sum of its children;
+        # the inverse with every tap the identity hands every child its parent's row
+        down = sparse_conv.SparseConv3d(C, C, 2, 2, bias=False, indice_key="d").to(dev)
+        up = sparse_conv.SparseInverseConv3d(C, C, 2, indice_key="d", bias=False).to(dev)
+        eye = torch.eye(C, device=dev).expand(8, C, C).contiguous()
+        down.weight.copy_(eye), up.weight.copy_(eye)
+        yd = down(x)
+        rb = x.indice_dict["d"]
+        has_parent = rb.parent >= 0
+        assert rel_err(yd.features.sum(0).cpu(), feats[has_parent].sum(0).cpu()) <= 1e-4
+        uniq = torch.unique(torch.cat([coords[has_parent][:, :1], coords[has_parent][:, 1:] // 2], 1), dim=0)
+        assert torch.equal(yd.indices.cpu(), uniq.cpu().to(torch.int32))
+        z = up(yd)
+        want = torch.zeros_like(feats)
+        want[has_parent] = yd.features[rb.parent[has_parent].long()]
+        assert torch.equal(z.features, want)
