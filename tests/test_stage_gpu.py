@@ -180,3 +180,25 @@ def test_stage_on_almost_empty_scenes(n_vox):
     if n_vox:
         ref = O.basic_layer(feats, coords, 1, dims, win, [_block_params(b) for b in layer.blocks], H)
         assert rel_err(y.features.cpu(), ref) <= 2e-4
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 3e-2)])
+def test_stage_at_full_size_fused_and_unfused_shell_agree(dtype, tol):
+    """The benchmark room (150 000 voxels), depth 2: the stage as built (two plans, one-pass shell)
+    against upstream's structure on the same kernels (every block buckets for itself, torch
+    LayerNorm and adds); both forms use the attention kernels the full-size parity tests pin."""
+    from sparseswin3d_b200 import scenes, stage
+
+    dev = torch.device("cuda:0")
+    coords_np, dims = scenes.room_scene(150_000, seed=0)
+    C, H, win = 96, 3, (7, 7, 7)
+    layer = stage.BasicLayer(dim=C, depth=2, num_heads=H, window_size=win, qkv_bias=True).to(dev)
+    _randomise(layer, 31)
+    layer = layer.to(dtype).eval()
+    feats = torch.randn(150_000, C, generator=torch.Generator().manual_seed(2)).to(dtype).to(dev)
+    x = stage.SparseVoxels(feats, torch.from_numpy(coords_np).to(dev), dims, 1)
+    with torch.no_grad():
+        a = layer(x).features
+        layer.reuse_plans, layer.fuse_shell = False, False
+        b = layer(x).features
+    assert rel_err(a.float().cpu(), b.float().cpu()) <= tol
